@@ -1,0 +1,411 @@
+// C ABI of humming_b200 (see include/humming_b200.h): argument validation,
+// launch planning, tensor-map encoding and kernel launches.  No entry point
+// here allocates device memory.
+#include "../../include/humming_b200.h"
+
+#include <cuda_runtime.h>
+#include <cudaTypedefs.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "gemm_w4a16.cuh"
+#include "prep.cuh"
+#include "sched.cuh"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define HM_CUDA_OK(expr)                                                                  \
+  do {                                                                                    \
+    cudaError_t _e = (expr);                                                              \
+    if (_e != cudaSuccess) return fail(HM_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(_e)); \
+  } while (0)
+
+inline bool is16(int dt) { return dt == HM_F16 || dt == HM_BF16; }
+
+int device_sm_count(int* out) {
+  static int cached[64] = {0};
+  int dev = 0;
+  HM_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(HM_ERR_CUDA, "device index %d out of range", dev);
+  if (cached[dev] == 0) {
+    int n = 0;
+    HM_CUDA_OK(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
+    cached[dev] = n;
+  }
+  *out = cached[dev];
+  return HM_OK;
+}
+
+PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) {
+      p = nullptr;
+    }
+    return reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+  }();
+  return fn;
+}
+
+int validate_desc(const hm_gemm_desc* d) {
+  if (d == nullptr) return fail(HM_ERR_INVALID, "desc is NULL");
+  if (d->shape_n <= 0 || d->shape_k <= 0) return fail(HM_ERR_INVALID, "shape_n/shape_k must be positive");
+  if (d->shape_n % hm::kTileN != 0) return fail(HM_ERR_INVALID, "shape_n=%d must be a multiple of 128", d->shape_n);
+  if (d->shape_k % hm::kBlockK != 0) return fail(HM_ERR_INVALID, "shape_k=%d must be a multiple of 64", d->shape_k);
+  if (d->group_size < 0) return fail(HM_ERR_INVALID, "group_size must be >= 0");
+  const int g = d->group_size == 0 ? d->shape_k : d->group_size;
+  if (d->shape_k % g != 0) return fail(HM_ERR_INVALID, "shape_k=%d not divisible by group_size=%d", d->shape_k, g);
+  if (is16(d->a_dtype)) {
+    if (d->b_dtype != HM_UINT(4) && d->b_dtype != HM_INT(4))
+      return fail(HM_ERR_UNSUPPORTED, "16-bit activations: weight dtype code 0x%x not built (uint4/int4 only)", d->b_dtype);
+    if (d->b_dtype == HM_INT(4) && d->has_zp) return fail(HM_ERR_INVALID, "dynamic zero point needs an unsigned weight dtype");
+    if (d->c_dtype != d->a_dtype) return fail(HM_ERR_UNSUPPORTED, "c_dtype must equal a_dtype for 16-bit activations");
+    if (d->bs_dtype != d->a_dtype) return fail(HM_ERR_UNSUPPORTED, "bs_dtype must equal a_dtype for 16-bit activations");
+    if (g % hm::kBlockK != 0) return fail(HM_ERR_UNSUPPORTED, "group_size=%d must be a multiple of 64", g);
+  } else {
+    return fail(HM_ERR_UNSUPPORTED, "a_dtype code %d not built", d->a_dtype);
+  }
+  if (d->m_tile != 0 && d->m_tile != 16 && d->m_tile != 32 && d->m_tile != 64 && d->m_tile != 128 && d->m_tile != 256)
+    return fail(HM_ERR_INVALID, "m_tile must be 0, 16, 32, 64, 128 or 256");
+  if (d->num_experts != 0) return fail(HM_ERR_UNSUPPORTED, "MoE layers go through hm_moe_gemm");
+  return HM_OK;
+}
+
+int make_plan(const hm_gemm_desc* d, int64_t m, hm_plan* plan) {
+  int rc = validate_desc(d);
+  if (rc != HM_OK) return rc;
+  if (m < 0 || m > (1ll << 30)) return fail(HM_ERR_INVALID, "m=%lld out of range", static_cast<long long>(m));
+  int sms = d->num_sms;
+  if (sms <= 0) {
+    rc = device_sm_count(&sms);
+    if (rc != HM_OK) return rc;
+  }
+  int mt = d->m_tile;
+  if (mt == 0) mt = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : m <= 128 ? 128 : 256;
+  memset(plan, 0, sizeof(*plan));
+  plan->m_tile = mt;
+  plan->n_tiles = d->shape_n / hm::kTileN;
+  plan->m_tiles = static_cast<int32_t>((m + mt - 1) / mt);
+  plan->kb_per_tile = d->shape_k / hm::kBlockK;
+  const int64_t tiles = static_cast<int64_t>(plan->n_tiles) * plan->m_tiles;
+  const int64_t units = tiles * plan->kb_per_tile;
+  if (units >= (1ll << 31)) return fail(HM_ERR_INVALID, "problem too large for 32-bit unit indices");
+  plan->total_units = units;
+  if (tiles == 0) {
+    plan->grid = 0;
+    plan->workspace_bytes = 256;
+    return HM_OK;
+  }
+  if ((d->flags & HM_FLAG_NO_SPLIT_K) || tiles >= 4ll * sms) {
+    plan->mode = 0;
+    plan->grid = static_cast<int32_t>(tiles < sms ? tiles : sms);
+    plan->units_per_cta = 0;
+    plan->workspace_bytes = 256;
+  } else {
+    plan->mode = 1;
+    const int64_t min_units = 4;  // do not cut work finer than 4 k-blocks per CTA
+    int64_t max_ctas = units / min_units;
+    if (max_ctas < 1) max_ctas = 1;
+    int64_t grid = max_ctas < sms ? max_ctas : sms;
+    const int64_t per = (units + grid - 1) / grid;
+    grid = (units + per - 1) / per;
+    plan->grid = static_cast<int32_t>(grid);
+    plan->units_per_cta = static_cast<int32_t>(per);
+    int64_t counters = ((tiles * 4 * 4 + 255) / 256) * 256;
+    plan->workspace_bytes = 256 + counters + grid * 2 * static_cast<int64_t>(mt) * hm::kTileN * 4;
+  }
+  return HM_OK;
+}
+
+hm::SchedParams sched_of(const hm_plan& pl) {
+  hm::SchedParams s;
+  s.n_tiles = pl.n_tiles;
+  s.m_tiles = pl.m_tiles;
+  s.kb_per_tile = pl.kb_per_tile;
+  s.mode = pl.mode;
+  s.grid = pl.grid;
+  s.units_per_cta = pl.units_per_cta;
+  s.total_units = static_cast<int>(pl.total_units);
+  return s;
+}
+
+template <int MT, bool BF16, bool HAS_ZP, bool A_TMEM>
+int launch_gemm(const hm::GemmParams& p, const CUtensorMap& tmap, int grid, cudaStream_t stream) {
+  using Cfg = hm::GemmCfg<MT, A_TMEM>;
+  auto kern = hm::gemm_w4a16_kernel<MT, BF16, HAS_ZP, A_TMEM>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  HM_CUDA_OK(cudaGetDevice(&dev));
+  if (!configured[dev & 63]) {
+    HM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_ALLOC));
+    configured[dev & 63] = true;
+  }
+  kern<<<grid, hm::kThreads, Cfg::SMEM_ALLOC, stream>>>(p, tmap);
+  HM_CUDA_OK(cudaGetLastError());
+  return HM_OK;
+}
+
+template <int MT>
+int dispatch_gemm(bool bf16, bool zp, bool a_tmem, const hm::GemmParams& p, const CUtensorMap& tmap, int grid,
+                  cudaStream_t stream) {
+  if (a_tmem) {
+    if (bf16) return zp ? launch_gemm<MT, true, true, true>(p, tmap, grid, stream) : launch_gemm<MT, true, false, true>(p, tmap, grid, stream);
+    return zp ? launch_gemm<MT, false, true, true>(p, tmap, grid, stream) : launch_gemm<MT, false, false, true>(p, tmap, grid, stream);
+  }
+  if (bf16) return zp ? launch_gemm<MT, true, true, false>(p, tmap, grid, stream) : launch_gemm<MT, true, false, false>(p, tmap, grid, stream);
+  return zp ? launch_gemm<MT, false, true, false>(p, tmap, grid, stream) : launch_gemm<MT, false, false, false>(p, tmap, grid, stream);
+}
+
+inline unsigned blocks_for(int64_t n, int threads) { return static_cast<unsigned>((n + threads - 1) / threads); }
+
+}  // namespace
+
+extern "C" {
+
+const char* hm_last_error(void) { return g_err; }
+int hm_version(void) { return 100; }
+
+int hm_pack_weight(const int32_t* codes, int32_t* packed, int64_t numel, int bits, void* stream) {
+  if (codes == nullptr || packed == nullptr) return fail(HM_ERR_INVALID, "NULL pointer");
+  if (bits < 1 || bits > 8) return fail(HM_ERR_INVALID, "bits=%d out of range 1..8", bits);
+  if (numel < 0 || numel % 32 != 0) return fail(HM_ERR_INVALID, "numel=%lld must be a multiple of 32", static_cast<long long>(numel));
+  if (numel == 0) return HM_OK;
+  const int64_t groups = numel / 32;
+  hm::pack_kernel<<<blocks_for(groups, 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      codes, reinterpret_cast<uint32_t*>(packed), groups, bits);
+  HM_CUDA_OK(cudaGetLastError());
+  return HM_OK;
+}
+
+int hm_unpack_weight(const int32_t* packed, int32_t* codes, int64_t numel, int bits, void* stream) {
+  if (codes == nullptr || packed == nullptr) return fail(HM_ERR_INVALID, "NULL pointer");
+  if (bits < 1 || bits > 8) return fail(HM_ERR_INVALID, "bits=%d out of range 1..8", bits);
+  if (numel < 0 || numel % 32 != 0) return fail(HM_ERR_INVALID, "numel=%lld must be a multiple of 32", static_cast<long long>(numel));
+  if (numel == 0) return HM_OK;
+  const int64_t groups = numel / 32;
+  hm::unpack_kernel<<<blocks_for(groups, 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint32_t*>(packed), codes, groups, bits);
+  HM_CUDA_OK(cudaGetLastError());
+  return HM_OK;
+}
+
+// The load-path entry points accept MoE descriptors (num_experts > 0): the
+// prepared layouts simply gain a leading expert dimension.
+static int validate_prepare(const hm_gemm_desc* d, int64_t* experts) {
+  if (d == nullptr) return fail(HM_ERR_INVALID, "desc is NULL");
+  hm_gemm_desc tmp = *d;
+  tmp.num_experts = 0;
+  int rc = validate_desc(&tmp);
+  if (rc != HM_OK) return rc;
+  if (d->num_experts < 0) return fail(HM_ERR_INVALID, "num_experts must be >= 0");
+  *experts = d->num_experts > 0 ? d->num_experts : 1;
+  return HM_OK;
+}
+
+int hm_repack_weight(const hm_gemm_desc* desc, const int32_t* packed, int32_t* out, void* stream) {
+  int64_t e = 1;
+  int rc = validate_prepare(desc, &e);
+  if (rc != HM_OK) return rc;
+  if (packed == nullptr || out == nullptr || packed == out) return fail(HM_ERR_INVALID, "packed/out NULL or aliased");
+  const int64_t words = e * desc->shape_n * (desc->shape_k / 8);
+  hm::repack_w4_kernel<<<blocks_for(words, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint32_t*>(packed), reinterpret_cast<uint32_t*>(out), words, desc->shape_n, desc->shape_k,
+      desc->b_dtype == HM_INT(4) ? 1 : 0);
+  HM_CUDA_OK(cudaGetLastError());
+  return HM_OK;
+}
+
+int hm_repack_scale(const hm_gemm_desc* desc, const void* scales, void* out, void* stream) {
+  int64_t e = 1;
+  int rc = validate_prepare(desc, &e);
+  if (rc != HM_OK) return rc;
+  if (scales == nullptr || out == nullptr || scales == out) return fail(HM_ERR_INVALID, "scales/out NULL or aliased");
+  const int g = desc->group_size == 0 ? desc->shape_k : desc->group_size;
+  const int groups = desc->shape_k / g;
+  const int64_t total = e * desc->shape_n * groups;
+  auto s = static_cast<cudaStream_t>(stream);
+  hm::repack_scale_kernel<uint16_t><<<blocks_for(total, 256), 256, 0, s>>>(
+      static_cast<const uint16_t*>(scales), static_cast<uint16_t*>(out), total, desc->shape_n, groups);
+  HM_CUDA_OK(cudaGetLastError());
+  return HM_OK;
+}
+
+int hm_repack_zero_point(const hm_gemm_desc* desc, const int32_t* zp, int32_t* out, void* stream) {
+  int64_t e = 1;
+  int rc = validate_prepare(desc, &e);
+  if (rc != HM_OK) return rc;
+  if (!desc->has_zp) return fail(HM_ERR_INVALID, "descriptor has no dynamic zero point");
+  if (zp == nullptr || out == nullptr || zp == out) return fail(HM_ERR_INVALID, "zp/out NULL or aliased");
+  const int g = desc->group_size == 0 ? desc->shape_k : desc->group_size;
+  const int groups = desc->shape_k / g;
+  const int64_t bytes = e * desc->shape_n * groups / 2;
+  hm::repack_zp4_kernel<<<blocks_for(bytes, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint32_t*>(zp), reinterpret_cast<uint8_t*>(out), bytes, desc->shape_n, groups);
+  HM_CUDA_OK(cudaGetLastError());
+  return HM_OK;
+}
+
+int hm_dequant_prepared(const hm_gemm_desc* desc, const void* w, const void* w_scale, const void* w_zp, float* out,
+                        void* stream) {
+  int64_t e = 1;
+  int rc = validate_prepare(desc, &e);
+  if (rc != HM_OK) return rc;
+  if (w == nullptr || w_scale == nullptr || out == nullptr) return fail(HM_ERR_INVALID, "NULL pointer");
+  if (desc->has_zp && w_zp == nullptr) return fail(HM_ERR_INVALID, "w_zp is NULL but the descriptor has zero points");
+  const int g = desc->group_size == 0 ? desc->shape_k : desc->group_size;
+  const int groups = desc->shape_k / g;
+  const int kbpg = g / hm::kBlockK;
+  const int64_t total = e * desc->shape_n * (desc->shape_k / hm::kBlockK);
+  auto s = static_cast<cudaStream_t>(stream);
+  const unsigned blocks = blocks_for(total, 128);
+  auto W = static_cast<const uint8_t*>(w);
+  auto S = static_cast<const uint8_t*>(w_scale);
+  auto Z = static_cast<const uint8_t*>(w_zp);
+  const bool bf16 = desc->a_dtype == HM_BF16;
+  if (bf16 && desc->has_zp) hm::dequant_prepared_w4a16_kernel<true, true><<<blocks, 128, 0, s>>>(W, S, Z, out, total, desc->shape_n, desc->shape_k, groups, kbpg);
+  else if (bf16) hm::dequant_prepared_w4a16_kernel<true, false><<<blocks, 128, 0, s>>>(W, S, Z, out, total, desc->shape_n, desc->shape_k, groups, kbpg);
+  else if (desc->has_zp) hm::dequant_prepared_w4a16_kernel<false, true><<<blocks, 128, 0, s>>>(W, S, Z, out, total, desc->shape_n, desc->shape_k, groups, kbpg);
+  else hm::dequant_prepared_w4a16_kernel<false, false><<<blocks, 128, 0, s>>>(W, S, Z, out, total, desc->shape_n, desc->shape_k, groups, kbpg);
+  HM_CUDA_OK(cudaGetLastError());
+  return HM_OK;
+}
+
+int hm_quant_input(const void* x, int x_dtype, int64_t m, int64_t k, int64_t ldx, int q_dtype, void* q, float* scales,
+                   void* stream) {
+  if (x == nullptr || q == nullptr || scales == nullptr) return fail(HM_ERR_INVALID, "NULL pointer");
+  if (q_dtype != HM_E4M3) return fail(HM_ERR_UNSUPPORTED, "only e4m3 activation quantization is built");
+  if (m < 0 || k <= 0 || ldx < k) return fail(HM_ERR_INVALID, "bad m/k/ldx");
+  if (m == 0) return HM_OK;
+  auto s = static_cast<cudaStream_t>(stream);
+  const unsigned grid = static_cast<unsigned>(m);
+  auto Q = static_cast<uint8_t*>(q);
+  if (x_dtype == HM_BF16) hm::quant_rowwise_e4m3_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), ldx, k, Q, scales);
+  else if (x_dtype == HM_F16) hm::quant_rowwise_e4m3_kernel<__half><<<grid, 256, 0, s>>>(static_cast<const __half*>(x), ldx, k, Q, scales);
+  else if (x_dtype == HM_F32) hm::quant_rowwise_e4m3_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(x), ldx, k, Q, scales);
+  else return fail(HM_ERR_INVALID, "x_dtype code %d not accepted", x_dtype);
+  HM_CUDA_OK(cudaGetLastError());
+  return HM_OK;
+}
+
+int hm_gemm_plan(const hm_gemm_desc* desc, int64_t m, hm_plan* plan) {
+  if (plan == nullptr) return fail(HM_ERR_INVALID, "plan is NULL");
+  return make_plan(desc, m, plan);
+}
+
+size_t hm_gemm_workspace_bytes(const hm_gemm_desc* desc, int64_t m) {
+  hm_plan pl;
+  if (make_plan(desc, m, &pl) != HM_OK) return 0;
+  return static_cast<size_t>(pl.workspace_bytes);
+}
+
+int hm_debug_schedule(const hm_plan* plan, int cta, int32_t* out, int cap) {
+  if (plan == nullptr || out == nullptr) return fail(HM_ERR_INVALID, "NULL pointer");
+  hm::SegIter it;
+  it.init(sched_of(*plan), cta);
+  hm::Segment s;
+  int n = 0;
+  while (it.next(s)) {
+    if (n < cap) {
+      int32_t* o = out + 7 * n;
+      o[0] = s.tile; o[1] = s.kb0; o[2] = s.kb1; o[3] = s.partial; o[4] = s.nseg; o[5] = s.first_cta; o[6] = s.slot;
+    }
+    ++n;
+  }
+  return n;
+}
+
+int hm_gemm(const hm_gemm_desc* desc, int64_t m, const void* a, int64_t lda, const float* a_scale, const void* w,
+            const void* w_scale, const void* w_zp, const void* bias, void* c, int64_t ldc, void* workspace,
+            size_t workspace_bytes, void* stream) {
+  hm_plan pl;
+  int rc = make_plan(desc, m, &pl);
+  if (rc != HM_OK) return rc;
+  if (m == 0) return HM_OK;
+  (void)a_scale;
+  if (a == nullptr || w == nullptr || w_scale == nullptr || c == nullptr) return fail(HM_ERR_INVALID, "NULL pointer");
+  if (desc->has_zp && w_zp == nullptr) return fail(HM_ERR_INVALID, "w_zp is NULL but the descriptor has zero points");
+  if (desc->has_bias && bias == nullptr) return fail(HM_ERR_INVALID, "bias is NULL but the descriptor has a bias");
+  if (lda < desc->shape_k || ldc < desc->shape_n) return fail(HM_ERR_INVALID, "lda/ldc smaller than the row length");
+  if ((reinterpret_cast<uintptr_t>(a) & 15) || ((lda * 2) & 15)) return fail(HM_ERR_INVALID, "activations must be 16-byte aligned with a 16-byte row pitch");
+  if ((reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(w_scale) & 15) || (reinterpret_cast<uintptr_t>(w_zp) & 15))
+    return fail(HM_ERR_INVALID, "prepared weight buffers must be 16-byte aligned");
+  if (workspace == nullptr || workspace_bytes < static_cast<size_t>(pl.workspace_bytes))
+    return fail(HM_ERR_WORKSPACE, "workspace of %zu bytes given, %lld needed", workspace_bytes, static_cast<long long>(pl.workspace_bytes));
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return fail(HM_ERR_INVALID, "workspace must be 256-byte aligned");
+
+  auto encode = tensor_map_encoder();
+  if (encode == nullptr) return fail(HM_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  CUtensorMap tmap;
+  const bool bf16 = desc->a_dtype == HM_BF16;
+  const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(desc->shape_k), static_cast<cuuint64_t>(m)};
+  const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(lda) * 2};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(hm::kBlockK), static_cast<cuuint32_t>(pl.m_tile)};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult cr = encode(&tmap, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                       const_cast<void*>(a), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (cr != CUDA_SUCCESS) return fail(HM_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", static_cast<int>(cr));
+
+  const int g = desc->group_size == 0 ? desc->shape_k : desc->group_size;
+  hm::GemmParams p;
+  p.w = static_cast<const uint8_t*>(w);
+  p.w_scale = static_cast<const uint8_t*>(w_scale);
+  p.w_zp = static_cast<const uint8_t*>(w_zp);
+  p.bias = desc->has_bias ? bias : nullptr;
+  p.c = c;
+  auto ws = static_cast<uint8_t*>(workspace);
+  p.status = reinterpret_cast<int*>(ws);
+  p.counters = reinterpret_cast<int*>(ws + 256);
+  const int64_t tiles = static_cast<int64_t>(pl.n_tiles) * pl.m_tiles;
+  const int64_t counters = ((tiles * 4 * 4 + 255) / 256) * 256;
+  p.partials = reinterpret_cast<float*>(ws + 256 + (pl.mode == 1 ? counters : 0));
+  p.M = static_cast<int>(m);
+  p.N = desc->shape_n;
+  p.K = desc->shape_k;
+  p.ldc = static_cast<int>(ldc);
+  p.groups = desc->shape_k / g;
+  p.kb_per_group = g / hm::kBlockK;
+  p.sched = sched_of(pl);
+
+  const bool a_tmem = !(desc->flags & HM_FLAG_A_OPERAND_SMEM);
+  auto s = static_cast<cudaStream_t>(stream);
+  switch (pl.m_tile) {
+    case 16: return dispatch_gemm<16>(bf16, desc->has_zp != 0, a_tmem, p, tmap, pl.grid, s);
+    case 32: return dispatch_gemm<32>(bf16, desc->has_zp != 0, a_tmem, p, tmap, pl.grid, s);
+    case 64: return dispatch_gemm<64>(bf16, desc->has_zp != 0, a_tmem, p, tmap, pl.grid, s);
+    case 128: return dispatch_gemm<128>(bf16, desc->has_zp != 0, a_tmem, p, tmap, pl.grid, s);
+    case 256: return dispatch_gemm<256>(bf16, desc->has_zp != 0, a_tmem, p, tmap, pl.grid, s);
+  }
+  return fail(HM_ERR_INVALID, "no kernel for m_tile=%d", pl.m_tile);
+}
+
+int hm_check_status(void* workspace, size_t workspace_bytes, void* stream) {
+  if (workspace == nullptr || workspace_bytes < 256) return fail(HM_ERR_WORKSPACE, "workspace missing");
+  auto s = static_cast<cudaStream_t>(stream);
+  int st[8];
+  HM_CUDA_OK(cudaMemcpyAsync(st, workspace, sizeof(st), cudaMemcpyDeviceToHost, s));
+  HM_CUDA_OK(cudaStreamSynchronize(s));
+  if (st[0] != 0) {
+    // Counters and partial slots may be half-updated: clear everything.
+    HM_CUDA_OK(cudaMemsetAsync(workspace, 0, workspace_bytes, s));
+    HM_CUDA_OK(cudaStreamSynchronize(s));
+    return fail(HM_ERR_DEVICE, "kernel aborted: code %d in CTA %d (detail %d, %d)", st[0], st[1], st[2], st[3]);
+  }
+  return HM_OK;
+}
+
+}  // extern "C"

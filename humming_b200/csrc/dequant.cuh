@@ -1,0 +1,64 @@
+// Weight decode shared by the GEMM main loop and the test-only
+// "dequantize prepared weights" kernel, so both produce identical bits.
+//
+// 4-bit integer codes, 16-bit activations.  Numerics follow the reference:
+//   w = rn16( (q - zp) * s )        with q - zp exact in the 16-bit type
+// (humming/include/humming/datatype/dequant_single.cuh:25-46 builds q and zp
+// with the magic-number trick, humming/include/humming/arith/mainloop_arith.cuh:117-161
+// multiplies by the scale with __hmul2) -- i.e. weight_ref rounded once to the
+// activation type, as humming/tests/test_scale.py:140-141 encodes.
+#pragma once
+#include "ptx.cuh"
+
+namespace hm {
+
+// Prepared nibble order inside one 32-bit word holding 8 consecutive K
+// elements e0..e7: nibble p (bits 4p..4p+3) holds element 2p for p < 4 and
+// element 2(p-4)+1 for p >= 4.  Then ((w >> 4i) & 0x000F000F) has element 2i in
+// its low half and 2i+1 in its high half: one shift + one lop3 per output pair.
+__host__ __device__ constexpr int prepared_nibble_pos(int e) { return (e & 1) ? 4 + (e >> 1) : (e >> 1); }
+
+template <bool BF16>
+HM_DEVICE uint32_t sub2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  if constexpr (BF16) {
+    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  } else {
+    asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  }
+  return d;
+}
+template <bool BF16>
+HM_DEVICE uint32_t mul2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  if constexpr (BF16) {
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  } else {
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  }
+  return d;
+}
+
+// 0x4300 = bf16 128.0 (ulp 1 up to 255); 0x6400 = fp16 1024.0 (ulp 1 up to 2047).
+template <bool BF16>
+struct Magic {
+  static constexpr uint32_t kBase = BF16 ? 0x43004300u : 0x64006400u;
+};
+
+// `zp_magic2`: (base + zero point) in both halves; `scale2`: the scale in both halves.
+template <bool BF16>
+HM_DEVICE void dequant_word_u4(uint32_t w, uint32_t zp_magic2, uint32_t scale2, uint32_t* out4) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint32_t t = lop3_and_or(w >> (4 * i), 0x000F000Fu, Magic<BF16>::kBase);
+    out4[i] = mul2<BF16>(sub2<BF16>(t, zp_magic2), scale2);
+  }
+}
+
+template <bool BF16>
+HM_DEVICE uint32_t zp_magic_pair(uint32_t zp) {
+  uint32_t h = (Magic<BF16>::kBase & 0xFFFFu) | zp;
+  return h | (h << 16);
+}
+
+}  // namespace hm

@@ -1,0 +1,208 @@
+// Load-path and helper kernels: bit packing, the finish_load repack into the
+// tile-interleaved layout, the test-only inverse (prepared -> fp32), and the
+// per-token FP8 activation quantizer.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+
+#include "dequant.cuh"
+#include "gemm_w4a16.cuh"
+
+namespace hm {
+
+// One thread packs 32 codes into `bits` words: element i occupies bits
+// [i*bits, (i+1)*bits) of the little-endian stream.
+// Same stream as humming/include/humming/kernel/pack_weight.cuh:5-27.
+__global__ void pack_kernel(const int32_t* __restrict__ in, uint32_t* __restrict__ out, int64_t ngroups, int bits) {
+  const int64_t g = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (g >= ngroups) return;
+  const uint32_t mask = (bits == 32) ? 0xFFFFFFFFu : ((1u << bits) - 1u);
+  uint32_t words[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) words[j] = 0;
+  for (int i = 0; i < 32; ++i) {
+    const uint32_t v = static_cast<uint32_t>(in[g * 32 + i]) & mask;
+    const int idx = i * bits;
+    const int w = idx >> 5;
+    const int off = idx & 31;
+    words[w] |= v << off;
+    if (off + bits > 32) words[w + 1] |= v >> (32 - off);
+  }
+  for (int j = 0; j < bits; ++j) out[g * bits + j] = words[j];
+}
+
+// Inverse of pack_kernel (humming/include/humming/kernel/pack_weight.cuh:29-50).
+__global__ void unpack_kernel(const uint32_t* __restrict__ in, int32_t* __restrict__ out, int64_t ngroups, int bits) {
+  const int64_t g = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (g >= ngroups) return;
+  const uint32_t mask = (1u << bits) - 1u;
+  uint32_t words[9];
+  for (int j = 0; j < bits; ++j) words[j] = in[g * bits + j];
+  words[bits] = 0;
+  for (int i = 0; i < 32; ++i) {
+    const int idx = i * bits;
+    const int w = idx >> 5;
+    const int off = idx & 31;
+    uint32_t v = words[w] >> off;
+    if (off + bits > 32) v |= words[w + 1] << (32 - off);
+    out[g * 32 + i] = static_cast<int32_t>(v & mask);
+  }
+}
+
+// 4-bit codes, K-major (E, N, K/8) words -> [e][n_tile][kb][half][row][4 words],
+// nibbles permuted per prepared_nibble_pos(); two's-complement int4 is turned
+// into offset-8 unsigned codes (xor 8) so the GEMM sees one format.
+__global__ void repack_w4_kernel(const uint32_t* __restrict__ in, uint32_t* __restrict__ out, int64_t total_words,
+                                 int N, int K, int is_signed) {
+  const int64_t o = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (o >= total_words) return;
+  const int KB = K / kBlockK;
+  const int n_tiles = N / kTileN;
+  const int wi = static_cast<int>(o & 3);
+  const int r = static_cast<int>((o >> 2) & 127);
+  const int h = static_cast<int>((o >> 9) & 1);
+  int64_t rest = o >> 10;
+  const int kb = static_cast<int>(rest % KB);
+  rest /= KB;
+  const int nt = static_cast<int>(rest % n_tiles);
+  const int64_t e = rest / n_tiles;
+  const int64_t n = static_cast<int64_t>(nt) * kTileN + r;
+  const int kword = kb * 8 + h * 4 + wi;
+  uint32_t w = in[(e * N + n) * (K / 8) + kword];
+  if (is_signed) w ^= 0x88888888u;
+  uint32_t v = 0;
+#pragma unroll
+  for (int el = 0; el < 8; ++el) v |= ((w >> (4 * el)) & 0xFu) << (4 * prepared_nibble_pos(el));
+  out[o] = v;
+}
+
+// (E, N, groups) -> [e][n_tile][group][128 rows]; element size 1, 2 or 4 bytes.
+template <typename T>
+__global__ void repack_scale_kernel(const T* __restrict__ in, T* __restrict__ out, int64_t total, int N, int groups) {
+  const int64_t o = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (o >= total) return;
+  const int n_tiles = N / kTileN;
+  const int r = static_cast<int>(o & 127);
+  int64_t rest = o >> 7;
+  const int g = static_cast<int>(rest % groups);
+  rest /= groups;
+  const int nt = static_cast<int>(rest % n_tiles);
+  const int64_t e = rest / n_tiles;
+  const int64_t n = static_cast<int64_t>(nt) * kTileN + r;
+  out[o] = in[(e * N + n) * groups + g];
+}
+
+// Zero points: nibble i of the flat (E, N, groups) element order lives in word
+// i/8 at bits 4*(i%8).  Output byte b of [e][n_tile][group][64] holds rows 2b
+// (low nibble) and 2b+1 (high nibble).
+__global__ void repack_zp4_kernel(const uint32_t* __restrict__ in, uint8_t* __restrict__ out, int64_t total_bytes,
+                                  int N, int groups) {
+  const int64_t o = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (o >= total_bytes) return;
+  const int n_tiles = N / kTileN;
+  const int b = static_cast<int>(o & 63);
+  int64_t rest = o >> 6;
+  const int g = static_cast<int>(rest % groups);
+  rest /= groups;
+  const int nt = static_cast<int>(rest % n_tiles);
+  const int64_t e = rest / n_tiles;
+  uint32_t byte = 0;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int64_t n = static_cast<int64_t>(nt) * kTileN + 2 * b + half;
+    const int64_t i = (e * N + n) * groups + g;
+    const uint32_t nib = (in[i >> 3] >> (4 * (i & 7))) & 0xFu;
+    byte |= nib << (4 * half);
+  }
+  out[o] = static_cast<uint8_t>(byte);
+}
+
+// Prepared buffers -> fp32 (E, N, K), one thread per (row, k-block), decoding
+// with the GEMM's own device function.
+template <bool BF16, bool HAS_ZP>
+__global__ void dequant_prepared_w4a16_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ w_scale,
+                                              const uint8_t* __restrict__ w_zp, float* __restrict__ out, int64_t total,
+                                              int N, int K, int groups, int kb_per_group) {
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t >= total) return;
+  const int KB = K / kBlockK;
+  const int n_tiles = N / kTileN;
+  const int r = static_cast<int>(t & 127);
+  int64_t rest = t >> 7;
+  const int kb = static_cast<int>(rest % KB);
+  rest /= KB;
+  const int nt = static_cast<int>(rest % n_tiles);
+  const int64_t e = rest / n_tiles;
+  const int g = kb / kb_per_group;
+  const uint8_t* codes = w + ((e * n_tiles + nt) * KB + kb) * static_cast<int64_t>(kCodeBytes);
+  const int64_t grp = (e * n_tiles + nt) * groups + g;
+  const uint4 lo = *reinterpret_cast<const uint4*>(codes + r * 16);
+  const uint4 hi = *reinterpret_cast<const uint4*>(codes + 2048 + r * 16);
+  const uint32_t sc16 = *reinterpret_cast<const uint16_t*>(w_scale + grp * kScaleBytes + r * 2);
+  const uint32_t scale2 = sc16 | (sc16 << 16);
+  uint32_t zp = 8;
+  if constexpr (HAS_ZP) zp = (w_zp[grp * kZpBytes + (r >> 1)] >> ((r & 1) * 4)) & 0xF;
+  const uint32_t zpm = zp_magic_pair<BF16>(zp);
+  uint32_t v[32];
+  const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) dequant_word_u4<BF16>(words[i], zpm, scale2, v + 4 * i);
+  float* dst = out + (e * N + static_cast<int64_t>(nt) * kTileN + r) * K + kb * kBlockK;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    float a, b;
+    if constexpr (BF16) {
+      a = __uint_as_float(v[i] << 16);
+      b = __uint_as_float(v[i] & 0xFFFF0000u);
+    } else {
+      const __half2 h2 = *reinterpret_cast<const __half2*>(&v[i]);
+      a = __low2float(h2);
+      b = __high2float(h2);
+    }
+    dst[2 * i] = a;
+    dst[2 * i + 1] = b;
+  }
+}
+
+// Per-token FP8 (e4m3) quantization: one CTA per row.
+// scale = max(absmax, 1e-30) / 448 ; q = e4m3_rn_satfinite(x * (1 / scale))
+// (humming/kernel/quant_input.py:11-14, :36-37, :133-141).
+template <typename T>
+__device__ __forceinline__ float to_float(T v);
+template <>
+__device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_float<__half>(__half v) { return __half2float(v); }
+template <>
+__device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__global__ void quant_rowwise_e4m3_kernel(const T* __restrict__ x, int64_t ldx, int64_t k, uint8_t* __restrict__ q,
+                                          float* __restrict__ scales) {
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x;
+  const T* xr = x + row * ldx;
+  float amax = 0.f;
+  for (int64_t i = threadIdx.x; i < k; i += blockDim.x) amax = fmaxf(amax, fabsf(to_float<T>(xr[i])));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = (threadIdx.x < (blockDim.x >> 5)) ? red[threadIdx.x] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    if (threadIdx.x == 0) red[0] = v;
+  }
+  __syncthreads();
+  const float scale = __fdiv_rn(fmaxf(red[0], 1e-30f), 448.f);
+  const float inv = __fdiv_rn(1.f, scale);
+  if (threadIdx.x == 0) scales[row] = scale;
+  for (int64_t i = threadIdx.x; i < k; i += blockDim.x) {
+    const float v = to_float<T>(xr[i]) * inv;
+    q[row * k + i] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
+  }
+}
+
+}  // namespace hm

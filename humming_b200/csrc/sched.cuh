@@ -1,0 +1,106 @@
+// Static tile scheduler shared by host (planning, tests) and device (every
+// warp role of a CTA replays the same segment sequence independently).
+//
+// Work is the grid of (tile, k-block) units, tile = (m_tile, n_tile) of
+// 128 weight rows x m_tile tokens, k-block = 64 elements of K.
+//   mode 0: whole tiles, CTA c takes tiles c, c+grid, c+2*grid, ...
+//   mode 1: the flattened unit range is cut into `grid` contiguous runs of
+//           units_per_cta units; a run may start and end inside a tile.  Such
+//           partial segments go to an fp32 workspace slot and the last CTA to
+//           finish a tile (atomic counter, no spinning) sums the slots in CTA
+//           order, so the result does not depend on arrival order.
+// Role of the reference's Scheduler (humming/include/humming/scheduler.cuh:55-155),
+// with the lock-ordered 16-bit accumulation replaced by fp32 partials.
+#pragma once
+#include <cstdint>
+
+namespace hm {
+
+#if defined(__CUDACC__)
+#define HM_HD __host__ __device__ __forceinline__
+#else
+#define HM_HD inline
+#endif
+
+struct SchedParams {
+  int n_tiles;
+  int m_tiles;
+  int kb_per_tile;
+  int mode;
+  int grid;
+  int units_per_cta;
+  int total_units;
+};
+
+struct Segment {
+  int tile;
+  int m_tile;
+  int n_tile;
+  int kb0;
+  int kb1;
+  int partial;    // 1: K range shorter than the tile's
+  int nseg;       // number of CTAs contributing to this tile (partial only)
+  int first_cta;  // first contributing CTA (partial only)
+  int slot;       // workspace slot of this segment: cta*2 + {0,1}
+};
+
+// Slot of CTA `cta`'s contribution to `tile`: its first tile uses slot 0, any
+// later (necessarily its last) partial tile slot 1.
+HM_HD int sched_slot(const SchedParams& p, int cta, int tile) {
+  int first_tile = (cta * p.units_per_cta) / p.kb_per_tile;
+  return cta * 2 + (tile == first_tile ? 0 : 1);
+}
+
+struct SegIter {
+  SchedParams p;
+  int cta;
+  int u;      // mode 1: next unit; mode 0: next tile
+  int u_end;
+
+  HM_HD void init(const SchedParams& params, int cta_) {
+    p = params;
+    cta = cta_;
+    if (p.mode == 0) {
+      u = cta;
+      u_end = p.n_tiles * p.m_tiles;
+    } else {
+      u = cta * p.units_per_cta;
+      int e = u + p.units_per_cta;
+      u_end = e < p.total_units ? e : p.total_units;
+    }
+  }
+
+  HM_HD bool next(Segment& s) {
+    if (u >= u_end) return false;
+    if (p.mode == 0) {
+      s.tile = u;
+      s.kb0 = 0;
+      s.kb1 = p.kb_per_tile;
+      s.partial = 0;
+      s.nseg = 1;
+      s.first_cta = cta;
+      s.slot = 0;
+      u += p.grid;
+    } else {
+      int t = u / p.kb_per_tile;
+      s.tile = t;
+      s.kb0 = u - t * p.kb_per_tile;
+      int len = u_end - u;
+      int room = p.kb_per_tile - s.kb0;
+      if (len > room) len = room;
+      s.kb1 = s.kb0 + len;
+      s.partial = len < p.kb_per_tile ? 1 : 0;
+      int first = (t * p.kb_per_tile) / p.units_per_cta;
+      int last = ((t + 1) * p.kb_per_tile - 1) / p.units_per_cta;
+      s.first_cta = first;
+      s.nseg = last - first + 1;
+      s.slot = sched_slot(p, cta, t);
+      u += len;
+    }
+    s.m_tile = s.tile / p.n_tiles;
+    s.n_tile = s.tile - s.m_tile * p.n_tiles;
+    return true;
+  }
+};
+
+}  // namespace hm

@@ -1,0 +1,432 @@
+"""``HummingLayer`` / ``HummingMethod`` / ``HummingLayerMeta`` with the reference's
+names, arguments and defaults (``humming/layer.py:21-68, :71-550, :553-583``),
+backed by the sm_100a library.
+
+Differences a caller can observe:
+
+* parameters have the reference's names, dtypes and shapes, but the byte layout
+  after ``finish_load`` is this library's tile-interleaved layout;
+* kernels are not JIT-compiled per M bucket: the native planner picks the token
+  tile and the K split from M on every call, so ``prepare_default_kernel_configs``
+  only records options (MoE flags, explicit tile overrides);
+* option combinations that are not built raise ``NotImplementedError`` when the
+  layer is created instead of computing something else.
+"""
+import dataclasses
+from typing import Optional
+
+import torch
+
+from humming_b200 import dtypes
+from humming_b200 import native
+from humming_b200 import runtime
+from humming_b200.utils.weight import prepare_humming_tensor_for_glu, quantize_weight
+
+_FLOAT_DTYPES = (torch.float16, torch.bfloat16, torch.float32)
+_M_TILES = (16, 32, 64, 128, 256)
+
+
+@dataclasses.dataclass
+class HummingLayerMeta(object):
+    a_dtype: dtypes.DataType
+    b_dtype: dtypes.DataType
+    c_dtype: dtypes.DataType
+    bs_dtype: dtypes.DataType
+    shape_n: int
+    shape_k: int
+    pad_shape_n: int = 0
+    pad_shape_k: int = 0
+    num_experts: Optional[int] = None
+    has_input_scale: Optional[bool] = None
+    has_weight_scale: bool = True
+    input_scale_group_size: int = 0
+    weight_scale_group_size: int = 0
+    has_dynamic_zp: bool = False
+    has_bias: bool = False
+    has_global_scale: bool = False
+    mma_type: Optional[str] = "mma"  # accepted for compatibility; tcgen05 is always used
+    sublayer_name: str = ""
+
+    def __post_init__(self):
+        for f in ("a_dtype", "b_dtype", "c_dtype", "bs_dtype"):
+            setattr(self, f, dtypes.DataType.from_str(getattr(self, f)))
+        if self.a_dtype.num_bits != 16 and self.has_input_scale is None:
+            self.has_input_scale = True
+        self._reject_unbuilt()
+
+    def _reject_unbuilt(self):
+        def no(what):
+            raise NotImplementedError(f"humming_b200: {what} is not built")
+
+        if self.pad_shape_n or self.pad_shape_k:
+            no("pad_shape_n / pad_shape_k")
+        if self.has_global_scale:
+            no("has_global_scale")
+        if not self.has_weight_scale:
+            no("has_weight_scale=False")
+        if self.input_scale_group_size:
+            no("grouped input scales")
+        if self.c_dtype not in (dtypes.float16, dtypes.bfloat16):
+            no(f"c_dtype={self.c_dtype}")
+        if self.a_dtype in (dtypes.float16, dtypes.bfloat16):
+            if self.b_dtype not in (dtypes.uint4, dtypes.int4):
+                no(f"b_dtype={self.b_dtype} with 16-bit activations")
+            if self.c_dtype != self.a_dtype or self.bs_dtype != self.a_dtype:
+                no("c_dtype / bs_dtype different from a 16-bit a_dtype")
+            g = self.weight_scale_group_size or self.shape_k
+            if g % 64:
+                no(f"weight_scale_group_size={g} (multiples of 64 only)")
+        else:
+            no(f"a_dtype={self.a_dtype}")
+        if self.shape_n % 128 or self.shape_k % 64:
+            no("shape_n not a multiple of 128 or shape_k not a multiple of 64")
+        if self.has_dynamic_zp and self.b_dtype.is_signed:
+            raise ValueError("dynamic zero point only supports uint weight dtypes")
+
+    @property
+    def name_prefix(self):
+        return self.sublayer_name + "_" if self.sublayer_name else ""
+
+    def _name(self, base):
+        return self.name_prefix + base
+
+    weight_name = property(lambda self: self._name("weight"))
+    zero_point_name = property(lambda self: self._name("zero_point"))
+    weight_scale_name = property(lambda self: self._name("weight_scale"))
+    global_scale_name = property(lambda self: self._name("global_scale"))
+    bias_name = property(lambda self: self._name("bias"))
+
+    @property
+    def group_size(self):
+        return self.weight_scale_group_size or self.shape_k
+
+    @property
+    def num_groups(self):
+        return self.shape_k // self.group_size
+
+
+def _flat_copy(dst: torch.Tensor, src: torch.Tensor, offset: int = 0):
+    src = src.to(dst.device).reshape(-1)
+    dst.view(-1)[offset:offset + src.numel()].copy_(src)
+
+
+class HummingMethod(torch.nn.Module):
+    """Stateless helpers operating on any module that holds the parameters
+    (lets a host framework keep several quantized GEMMs on one module through
+    ``sublayer_name``), as in the reference (``humming/layer.py:71-550``)."""
+
+    # ------------------------------------------------------------------ params
+    @classmethod
+    def set_param(cls, layer: torch.nn.Module, name: str, data: torch.Tensor):
+        setattr(layer, name, torch.nn.Parameter(data, requires_grad=False))
+
+    @classmethod
+    def set_param_data(cls, layer, name: str, data: torch.Tensor, offset: Optional[int] = None,
+                       expert_id: Optional[int] = None):
+        """Copy ``data`` flat into parameter ``name`` (optionally into one expert's
+        slice, starting ``offset`` elements in)."""
+        param = getattr(layer, name, None)
+        if param is None:
+            return
+        assert data.dtype == param.dtype, f"{name}: {data.dtype} != {param.dtype}"
+        if name.endswith("bias"):
+            is_moe = param.ndim == 2
+        elif name.endswith("global_scale"):
+            is_moe = param.nelement() > 1
+        else:
+            is_moe = param.ndim == 3
+        if is_moe and expert_id is None and data.nelement() != param.nelement():
+            for e in range(data.size(0)):
+                _flat_copy(param.data[e], data[e], offset or 0)
+        else:
+            _flat_copy(param.data if expert_id is None else param.data[expert_id], data, offset or 0)
+
+    @classmethod
+    def create_weights(cls, layer: torch.nn.Module, meta: HummingLayerMeta):
+        """Allocate the parameters with the reference's shapes
+        (``humming/layer.py:110-158``): ``weight`` int32 ``(K/pk, N*pk*bits/32)``
+        with ``pk = 256/a_bits``, ``weight_scale`` ``(K/g, N)``, ``zero_point`` int32
+        ``(K/g, N*zpbits/32)``, ``bias`` ``(N,)``; MoE adds a leading expert dim."""
+        pk = 256 // meta.a_dtype.num_bits
+        lead = () if meta.num_experts is None else (meta.num_experts,)
+        weight_shape = lead + (meta.shape_k // pk, meta.shape_n * pk * meta.b_dtype.num_bits // 32)
+        cls.set_param(layer, meta.weight_name, torch.empty(weight_shape, dtype=torch.int32))
+        if meta.has_weight_scale:
+            bs_torch = dtypes.torch_dtype_map[meta.bs_dtype]
+            cls.set_param(layer, meta.weight_scale_name,
+                          torch.empty(lead + (meta.num_groups, meta.shape_n), dtype=bs_torch))
+            if meta.has_dynamic_zp:
+                zp_bits = 4 if meta.b_dtype.num_bits <= 4 else 8
+                cls.set_param(layer, meta.zero_point_name,
+                              torch.empty(lead + (meta.num_groups, meta.shape_n * zp_bits // 32), dtype=torch.int32))
+        if meta.has_bias:
+            cls.set_param(layer, meta.bias_name,
+                          torch.empty(lead + (meta.shape_n,), dtype=dtypes.torch_dtype_map[meta.c_dtype]))
+        # Kept for drop-in compatibility (reference humming/layer.py:154).  This
+        # library's own scratch is `humming_workspace`, sized from the launch plan.
+        layer.locks = torch.nn.Buffer(torch.zeros(1024, dtype=torch.int32))
+        for attr in ("humming_metas", "humming_kernel_options", "humming_block_size_configs", "humming_prepared"):
+            if not hasattr(layer, attr):
+                setattr(layer, attr, {})
+        layer.humming_metas[meta.sublayer_name] = meta
+        layer.humming_kernel_options[meta.sublayer_name] = {}
+        layer.humming_block_size_configs[meta.sublayer_name] = []
+        layer.humming_prepared[meta.sublayer_name] = False
+
+    @classmethod
+    def pad_tensor(cls, tensor: torch.Tensor, target_size: int) -> torch.Tensor:
+        value = 127 if tensor.dtype == torch.float8_e8m0fnu else 0
+        return torch.nn.functional.pad(tensor, pad=(0, target_size - tensor.size(-1)), value=value)
+
+    # ------------------------------------------------------------------ loading
+    @classmethod
+    def load_weight(cls, layer, weight=None, weight_scale=None, zero_point=None, global_scale=None, bias=None,
+                    offset_n: Optional[int] = None, expert_id: Optional[int] = None, sublayer_name: str = "",
+                    packed: bool = False, padded: bool = False):
+        """Checkpoint-shaped loading (``humming/layer.py:169-326``).
+
+        ``weight``: int32 codes ``([E,] N, K)`` (or packed ``([E,] N, K*bits/32)``
+        with ``packed=True``), or a float tensor to quantize on the fly;
+        ``weight_scale``: ``([E,] N, K/g)``; ``zero_point``: int32 ``([E,] N, K/g)``;
+        ``bias``: ``([E,] N)``.  ``offset_n`` loads an N-shard of a fused weight,
+        ``expert_id`` a single expert.  Must precede ``finish_load``.
+        """
+        meta: HummingLayerMeta = layer.humming_metas[sublayer_name]
+        if layer.humming_prepared[sublayer_name]:
+            raise RuntimeError("load_weight after finish_load")
+        if global_scale is not None:
+            raise NotImplementedError("humming_b200: global scale is not built")
+        n_total, k_total, bits = meta.shape_n, meta.shape_k, meta.b_dtype.num_bits
+        lead = (meta.num_experts,) if (meta.num_experts is not None and expert_id is None) else ()
+
+        if weight is not None and weight.dtype in _FLOAT_DTYPES:
+            assert weight_scale is None and zero_point is None
+            q_dtype = dtypes.InergerType(False, bits) if meta.b_dtype.is_integer_type else meta.b_dtype
+            q, s, z, _ = quantize_weight(weight.cuda(), dtype=q_dtype, scale_dtype=meta.bs_dtype,
+                                         group_size=meta.weight_scale_group_size, has_dynamic_zp=meta.has_dynamic_zp)
+            if meta.b_dtype.is_integer_type and meta.b_dtype.is_signed:
+                q = q - 2 ** (bits - 1)
+            return cls.load_weight(layer, weight=q, weight_scale=s, zero_point=z, bias=bias, offset_n=offset_n,
+                                   expert_id=expert_id, sublayer_name=sublayer_name)
+
+        if weight is not None:
+            assert weight.dtype == torch.int32
+            n_part = n_total if offset_n is None else weight.size(-2)
+            expect = lead + (n_part, k_total * bits // 32 if packed else k_total)
+            assert tuple(weight.shape) == expect, f"weight shape {tuple(weight.shape)} != {expect}"
+            if not packed:
+                weight = runtime.pack_weight(weight.cuda().contiguous(), bits)
+            cls.set_param_data(layer, meta.weight_name, weight, (offset_n or 0) * k_total * bits // 32, expert_id)
+
+        if weight_scale is not None:
+            param = getattr(layer, meta.weight_scale_name)
+            n_part = n_total if offset_n is None else weight_scale.size(-2)
+            expect = lead + (n_part, meta.num_groups)
+            assert tuple(weight_scale.shape) == expect, f"weight_scale shape {tuple(weight_scale.shape)} != {expect}"
+            if weight_scale.element_size() == 1 or param.element_size() == 1:
+                assert weight_scale.dtype == param.dtype
+            else:
+                assert weight_scale.dtype in _FLOAT_DTYPES
+                weight_scale = weight_scale.to(param.dtype)
+            cls.set_param_data(layer, meta.weight_scale_name, weight_scale, (offset_n or 0) * meta.num_groups, expert_id)
+
+        if zero_point is not None:
+            assert zero_point.dtype == torch.int32
+            if bits > 4:
+                raise NotImplementedError("zero points wider than 4 bits are not built")
+            if packed:
+                # reference packed form: (N*bits/32, K/g), packed along N
+                zp = zero_point.cuda().transpose(-1, -2).contiguous()
+                zp = runtime.unpack_weight(zp, bits).transpose(-1, -2).contiguous()
+            else:
+                zp = zero_point.cuda().contiguous()
+            n_part = n_total if offset_n is None else zp.size(-2)
+            expect = lead + (n_part, meta.num_groups)
+            assert tuple(zp.shape) == expect, f"zero_point shape {tuple(zp.shape)} != {expect}"
+            elem_offset = (offset_n or 0) * meta.num_groups
+            if (n_part * meta.num_groups) % 32 or elem_offset % 8:
+                raise ValueError("a zero-point shard must cover a multiple of 32 (row, group) entries")
+            # staging form: 4-bit codes packed 8 per int32 in (N, K/g) element order
+            zp_words = runtime.pack_weight(zp.view(*lead, -1) if lead else zp.view(-1), 4)
+            cls.set_param_data(layer, meta.zero_point_name, zp_words, elem_offset // 8, expert_id)
+
+        if bias is not None:
+            param = getattr(layer, meta.bias_name)
+            n_part = n_total if offset_n is None else bias.size(-1)
+            assert tuple(bias.shape) == lead + (n_part,)
+            assert bias.dtype in _FLOAT_DTYPES
+            cls.set_param_data(layer, meta.bias_name, bias.to(param.dtype), offset_n, expert_id)
+
+    @classmethod
+    def _desc(cls, meta: HummingLayerMeta, **over) -> native.GemmDesc:
+        kw = dict(shape_n=meta.shape_n, shape_k=meta.shape_k, a_dtype=meta.a_dtype, b_dtype=meta.b_dtype,
+                  c_dtype=meta.c_dtype, bs_dtype=meta.bs_dtype, group_size=meta.weight_scale_group_size,
+                  has_zp=meta.has_dynamic_zp, has_bias=meta.has_bias, num_experts=meta.num_experts or 0)
+        kw.update(over)
+        return runtime.make_desc(**kw)
+
+    @classmethod
+    def finish_load(cls, layer, should_preprocess_for_glu: bool = False, sublayer_name: str = ""):
+        """Repack the staged checkpoint data into the layout the GEMM streams
+        (``humming/layer.py:328-401``): codes tile-interleaved per
+        (128 rows x 64 K), scales and zero points tile-contiguous per group."""
+        meta: HummingLayerMeta = layer.humming_metas[sublayer_name]
+        if layer.humming_prepared[sublayer_name]:
+            raise RuntimeError("finish_load called twice")
+        weight = getattr(layer, meta.weight_name)
+        if not weight.is_cuda:
+            raise RuntimeError("move the layer to a CUDA device before finish_load (no CPU path)")
+        scale = getattr(layer, meta.weight_scale_name, None)
+        zp = getattr(layer, meta.zero_point_name, None)
+        bias = getattr(layer, meta.bias_name, None)
+        e = meta.num_experts or 1
+        n, k, bits = meta.shape_n, meta.shape_k, meta.b_dtype.num_bits
+        desc = cls._desc(meta)
+
+        w_rows = weight.data.view(e, n, k * bits // 32)
+        s_rows = scale.data.view(e, n, meta.num_groups) if scale is not None else None
+        zp_rows = None
+        if zp is not None:
+            zp_rows = runtime.unpack_weight(zp.data.view(e, -1).contiguous(), 4).view(e, n, meta.num_groups)
+        if should_preprocess_for_glu:
+            w_rows = prepare_humming_tensor_for_glu(w_rows, n, meta.pad_shape_n, True)
+            s_rows = prepare_humming_tensor_for_glu(s_rows, n, meta.pad_shape_n, True)
+            zp_rows = prepare_humming_tensor_for_glu(zp_rows, n, meta.pad_shape_n, True)
+            if bias is not None:
+                bias.data.copy_(prepare_humming_tensor_for_glu(bias.data.view(e, n), n, meta.pad_shape_n, True).view_as(bias))
+
+        weight.data.copy_(runtime.repack_weight(desc, w_rows.contiguous()).view_as(weight))
+        if s_rows is not None:
+            scale.data.copy_(runtime.repack_scale(desc, s_rows.contiguous()).view_as(scale))
+        if zp_rows is not None:
+            zp_words = runtime.pack_weight(zp_rows.contiguous().view(e, -1), 4)
+            zp.data.copy_(runtime.repack_zero_point(desc, zp_words).view_as(zp))
+        layer.humming_prepared[sublayer_name] = True
+
+    # ------------------------------------------------------------------ configs
+    @classmethod
+    def prepare_default_kernel_configs(cls, layer, sublayer_name: str = "", **kwargs):
+        """Record launch options (``is_moe``, ``top_k``, ``is_moe_down``,
+        ``activation_type``, ``use_stream_k`` ...).  The reference compiles six
+        M-bucket kernels here (``humming/layer.py:403-451``); this library plans
+        tile size and K split natively per call, so no buckets are installed."""
+        opts = layer.humming_kernel_options[sublayer_name]
+        opts.update(kwargs)
+        act = opts.get("activation_type")
+        if act not in (None, "none"):
+            raise NotImplementedError(f"humming_b200: fused activation {act!r} is not built")
+
+    @classmethod
+    def add_kernel_config(cls, layer, min_shape_m: int, max_shape_m: int, block_shape, warp_shape=None,
+                          sublayer_name: str = "", **kwargs):
+        """Force a token tile for ``min_shape_m <= M <= max_shape_m``
+        (``humming/layer.py:453-499``).  ``block_shape[0]`` is rounded up to a
+        tile this library has (16, 32, 64, 128, 256); N/K block sizes and
+        ``warp_shape`` have no counterpart and are ignored."""
+        m_tile = next((t for t in _M_TILES if t >= block_shape[0]), 256)
+        layer.humming_block_size_configs[sublayer_name] += [min_shape_m, max_shape_m, m_tile]
+        layer.humming_kernel_options[sublayer_name].update(kwargs)
+
+    # ------------------------------------------------------------------ forward
+    @classmethod
+    def may_quant_input(cls, meta: HummingLayerMeta, inputs: torch.Tensor, input_scale: Optional[torch.Tensor] = None):
+        if meta.a_dtype.num_bits == 16:
+            return inputs, None
+        if input_scale is not None:
+            return inputs, input_scale
+        return runtime.quant_input(inputs, str(meta.a_dtype))
+
+    @classmethod
+    def _workspace(cls, layer, nbytes: int, device) -> torch.Tensor:
+        ws = getattr(layer, "humming_workspace", None)
+        if ws is None or ws.numel() < nbytes or ws.device != device:
+            ws = torch.zeros(max(nbytes, 1 << 16), dtype=torch.uint8, device=device)
+            layer.humming_workspace = ws
+        return ws
+
+    @classmethod
+    def forward_layer(cls, layer, inputs: torch.Tensor, outputs: Optional[torch.Tensor] = None,
+                      input_scale: Optional[torch.Tensor] = None, topk_weights: Optional[torch.Tensor] = None,
+                      sorted_token_ids: Optional[torch.Tensor] = None, expert_ids: Optional[torch.Tensor] = None,
+                      num_tokens_post_padded: Optional[torch.Tensor] = None, sublayer_name: str = ""):
+        """``C = A . dequant(W)^T (+ bias)`` on the current stream
+        (``humming/layer.py:519-550``).  Asynchronous; concurrent forwards of the
+        same layer on different streams share one workspace and are not supported
+        (the reference has the same rule for ``locks``)."""
+        meta: HummingLayerMeta = layer.humming_metas[sublayer_name]
+        if not layer.humming_prepared[sublayer_name]:
+            raise RuntimeError("call finish_load before forward")
+        if meta.num_experts is not None or sorted_token_ids is not None:
+            raise NotImplementedError("humming_b200: the MoE (indexed) GEMM is not built yet")
+        inputs, input_scale = cls.may_quant_input(meta, inputs, input_scale)
+        a = inputs.reshape(-1, inputs.size(-1))
+        if a.stride(-1) != 1 or (a.stride(0) * a.element_size()) % 16 or a.data_ptr() % 16:
+            a = a.contiguous()
+        m = a.size(0)
+        if a.size(1) != meta.shape_k:
+            raise ValueError(f"inputs have K={a.size(1)}, layer expects {meta.shape_k}")
+        if a.dtype != dtypes.torch_dtype_map[meta.a_dtype]:
+            raise ValueError(f"inputs are {a.dtype}, layer expects {meta.a_dtype}")
+
+        m_tile = 0
+        cfg = layer.humming_block_size_configs[sublayer_name]
+        for i in range(0, len(cfg), 3):
+            if cfg[i] <= m <= cfg[i + 1]:
+                m_tile = cfg[i + 2]
+                break
+        opts = layer.humming_kernel_options[sublayer_name]
+        flags = 0 if opts.get("use_stream_k", True) else native.HM_FLAG_NO_SPLIT_K
+        flags |= opts.get("native_flags", 0)
+        desc = cls._desc(meta, m_tile=m_tile, flags=flags)
+
+        c_dtype = dtypes.torch_dtype_map[meta.c_dtype]
+        out_shape = inputs.shape[:-1] + (meta.shape_n,)
+        if outputs is None:
+            outputs = torch.empty(out_shape, dtype=c_dtype, device=a.device)
+        else:
+            assert outputs.dtype == c_dtype and outputs.is_contiguous() and tuple(outputs.shape) == tuple(out_shape)
+        if m == 0:
+            return outputs
+        ws = cls._workspace(layer, runtime.workspace_bytes(desc, m), a.device)
+        runtime.gemm(desc, a, getattr(layer, meta.weight_name), getattr(layer, meta.weight_scale_name, None),
+                     getattr(layer, meta.zero_point_name, None), getattr(layer, meta.bias_name, None),
+                     outputs.view(-1, meta.shape_n), ws, a_scale=input_scale)
+        return outputs
+
+    @classmethod
+    def check_status(cls, layer):
+        """Synchronise and raise if any kernel of this layer reported an abort."""
+        ws = getattr(layer, "humming_workspace", None)
+        if ws is not None:
+            runtime.check_status(ws)
+
+
+class HummingLayer(torch.nn.Module):
+    """One quantized linear layer (``humming/layer.py:553-583``)::
+
+        layer = HummingLayer(shape_n=…, shape_k=…, a_dtype=…, b_dtype=…, c_dtype=…, bs_dtype=…,
+                             weight_scale_group_size=128).cuda()
+        layer.load_weight(weight=codes, weight_scale=scales)
+        layer.finish_load()
+        out = layer(inputs=x)
+    """
+
+    def __init__(self, **kwargs):
+        super().__init__()
+        self.meta = HummingLayerMeta(**kwargs)
+        HummingMethod.create_weights(self, self.meta)
+
+    def load_weight(self, weight=None, weight_scale=None, zero_point=None, global_scale=None, bias=None,
+                    expert_id: Optional[int] = None):
+        HummingMethod.load_weight(layer=self, weight=weight, weight_scale=weight_scale, zero_point=zero_point,
+                                  global_scale=global_scale, bias=bias, expert_id=expert_id)
+
+    def finish_load(self):
+        HummingMethod.finish_load(self)
+        HummingMethod.prepare_default_kernel_configs(self)
+
+    def forward(self, **kwargs):
+        return HummingMethod.forward_layer(self, **kwargs)
+
+    def check_status(self):
+        HummingMethod.check_status(self)

@@ -1,0 +1,94 @@
+"""ctypes binding of the C ABI in ``include/humming_b200.h``.
+
+The library is loaded at import and every declared symbol is resolved
+immediately, so a missing or stale build fails here, loudly, rather than at the
+first forward.  There is no fallback implementation.
+"""
+import ctypes
+import os
+
+LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libhumming_b200.so")
+
+HM_OK = 0
+HM_ERR_INVALID = -1
+HM_ERR_UNSUPPORTED = -2
+HM_ERR_WORKSPACE = -3
+HM_ERR_CUDA = -4
+HM_ERR_DEVICE = -5
+
+HM_FLAG_A_OPERAND_SMEM = 1
+HM_FLAG_NO_SPLIT_K = 2
+
+
+class GemmDesc(ctypes.Structure):
+    """``hm_gemm_desc``."""
+
+    _fields_ = [(n, ctypes.c_int32) for n in (
+        "shape_n", "shape_k", "a_dtype", "b_dtype", "c_dtype", "bs_dtype", "group_size", "has_zp", "has_bias",
+        "num_experts", "top_k", "is_moe_down", "m_tile", "num_sms", "flags")]
+
+
+class Plan(ctypes.Structure):
+    """``hm_plan``."""
+
+    _fields_ = [(n, ctypes.c_int32) for n in (
+        "m_tile", "n_tiles", "m_tiles", "kb_per_tile", "mode", "grid", "units_per_cta", "reserved")] + [
+        ("total_units", ctypes.c_int64), ("workspace_bytes", ctypes.c_int64)]
+
+
+_P = ctypes.c_void_p
+_I = ctypes.c_int
+_L = ctypes.c_int64
+_DESC = ctypes.POINTER(GemmDesc)
+
+# name -> (restype, argtypes); one entry per HM_API declaration of the header.
+SIGNATURES = {
+    "hm_pack_weight": (_I, [_P, _P, _L, _I, _P]),
+    "hm_unpack_weight": (_I, [_P, _P, _L, _I, _P]),
+    "hm_repack_weight": (_I, [_DESC, _P, _P, _P]),
+    "hm_repack_scale": (_I, [_DESC, _P, _P, _P]),
+    "hm_repack_zero_point": (_I, [_DESC, _P, _P, _P]),
+    "hm_dequant_prepared": (_I, [_DESC, _P, _P, _P, _P, _P]),
+    "hm_quant_input": (_I, [_P, _I, _L, _L, _L, _I, _P, _P, _P]),
+    "hm_gemm_plan": (_I, [_DESC, _L, ctypes.POINTER(Plan)]),
+    "hm_gemm_workspace_bytes": (ctypes.c_size_t, [_DESC, _L]),
+    "hm_gemm": (_I, [_DESC, _L, _P, _L, _P, _P, _P, _P, _P, _P, _L, _P, ctypes.c_size_t, _P]),
+    "hm_check_status": (_I, [_P, ctypes.c_size_t, _P]),
+    "hm_last_error": (ctypes.c_char_p, []),
+    "hm_version": (_I, []),
+    "hm_debug_schedule": (_I, [ctypes.POINTER(Plan), _I, ctypes.POINTER(ctypes.c_int32), _I]),
+}
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        f"{LIB_PATH} is missing: build it with `python -m humming_b200.build` "
+        "(humming_b200 has no CPU or PyTorch fallback)")
+
+lib = ctypes.CDLL(LIB_PATH)
+for _name, (_res, _args) in SIGNATURES.items():
+    _fn = getattr(lib, _name)  # AttributeError here = stale build
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+
+class HummingError(RuntimeError):
+    def __init__(self, code, message):
+        super().__init__(f"humming_b200 error {code}: {message}")
+        self.code = code
+
+
+def last_error():
+    return lib.hm_last_error().decode()
+
+
+def check(code):
+    """Raise for a negative status: ValueError for bad arguments,
+    NotImplementedError for combinations that are not built, RuntimeError otherwise."""
+    if code >= 0:
+        return code
+    msg = last_error()
+    if code == HM_ERR_INVALID:
+        raise ValueError(msg)
+    if code == HM_ERR_UNSUPPORTED:
+        raise NotImplementedError(msg)
+    raise HummingError(code, msg)

@@ -1,0 +1,156 @@
+"""Tensor-level wrappers over the C ABI: turn torch tensors into raw pointers,
+pick the current CUDA stream, check status codes.  torch is used here for
+device memory and streams only; all arithmetic happens in the native library.
+"""
+import ctypes
+from typing import Optional
+
+import torch
+
+from humming_b200 import dtypes
+from humming_b200 import native
+
+_TORCH_TO_NATIVE = {torch.float16: 1, torch.bfloat16: 2, torch.float32: 3}
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream(device) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("humming_b200 runs on CUDA tensors only (there is no CPU path)")
+
+
+def make_desc(shape_n, shape_k, a_dtype, b_dtype, c_dtype, bs_dtype, group_size=0, has_zp=False, has_bias=False,
+              num_experts=0, top_k=0, is_moe_down=False, m_tile=0, num_sms=0, flags=0) -> native.GemmDesc:
+    as_dt = dtypes.DataType.from_str
+    return native.GemmDesc(
+        shape_n=shape_n, shape_k=shape_k,
+        a_dtype=as_dt(a_dtype).to_native(), b_dtype=as_dt(b_dtype).to_native(),
+        c_dtype=as_dt(c_dtype).to_native(), bs_dtype=as_dt(bs_dtype).to_native(),
+        group_size=group_size or 0, has_zp=int(bool(has_zp)), has_bias=int(bool(has_bias)),
+        num_experts=num_experts or 0, top_k=top_k or 0, is_moe_down=int(bool(is_moe_down)),
+        m_tile=m_tile, num_sms=num_sms, flags=flags)
+
+
+def pack_weight(codes: torch.Tensor, bits: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """int32 codes (…, K) -> packed int32 (…, K*bits/32)."""
+    _require_cuda(codes)
+    assert codes.dtype == torch.int32 and codes.is_contiguous()
+    k = codes.size(-1)
+    if k * bits % 32 != 0 or codes.nelement() % 32 != 0:
+        raise ValueError("the number of codes must be a multiple of 32")
+    shape = codes.shape[:-1] + (k * bits // 32,)
+    if out is None:
+        out = torch.empty(shape, dtype=torch.int32, device=codes.device)
+    assert out.shape == shape and out.is_contiguous() and out.dtype == torch.int32
+    with torch.cuda.device(codes.device):
+        native.check(native.lib.hm_pack_weight(_ptr(codes), _ptr(out), codes.nelement(), bits, _stream(codes.device)))
+    return out
+
+
+def unpack_weight(packed: torch.Tensor, bits: int) -> torch.Tensor:
+    """Inverse of :func:`pack_weight`."""
+    _require_cuda(packed)
+    assert packed.dtype == torch.int32 and packed.is_contiguous()
+    words = packed.size(-1)
+    if words * 32 % bits != 0:
+        raise ValueError("packed row length does not hold a whole number of codes")
+    out = torch.empty(packed.shape[:-1] + (words * 32 // bits,), dtype=torch.int32, device=packed.device)
+    if out.nelement() % 32 != 0:
+        raise ValueError("the number of codes must be a multiple of 32")
+    with torch.cuda.device(packed.device):
+        native.check(native.lib.hm_unpack_weight(_ptr(packed), _ptr(out), out.nelement(), bits, _stream(packed.device)))
+    return out
+
+
+def repack_weight(desc: native.GemmDesc, packed: torch.Tensor) -> torch.Tensor:
+    _require_cuda(packed)
+    assert packed.dtype == torch.int32 and packed.is_contiguous()
+    out = torch.empty_like(packed)
+    with torch.cuda.device(packed.device):
+        native.check(native.lib.hm_repack_weight(ctypes.byref(desc), _ptr(packed), _ptr(out), _stream(packed.device)))
+    return out
+
+
+def repack_scale(desc: native.GemmDesc, scales: torch.Tensor) -> torch.Tensor:
+    _require_cuda(scales)
+    assert scales.is_contiguous()
+    out = torch.empty_like(scales)
+    with torch.cuda.device(scales.device):
+        native.check(native.lib.hm_repack_scale(ctypes.byref(desc), _ptr(scales), _ptr(out), _stream(scales.device)))
+    return out
+
+
+def repack_zero_point(desc: native.GemmDesc, zp: torch.Tensor) -> torch.Tensor:
+    _require_cuda(zp)
+    assert zp.dtype == torch.int32 and zp.is_contiguous()
+    out = torch.empty_like(zp)
+    with torch.cuda.device(zp.device):
+        native.check(native.lib.hm_repack_zero_point(ctypes.byref(desc), _ptr(zp), _ptr(out), _stream(zp.device)))
+    return out
+
+
+def dequant_prepared(desc: native.GemmDesc, w, w_scale, w_zp=None) -> torch.Tensor:
+    """Prepared buffers -> fp32 (E, N, K) (or (N, K) for a dense descriptor)."""
+    _require_cuda(w, w_scale, w_zp)
+    e = max(desc.num_experts, 1)
+    out = torch.empty((e, desc.shape_n, desc.shape_k), dtype=torch.float32, device=w.device)
+    with torch.cuda.device(w.device):
+        native.check(native.lib.hm_dequant_prepared(ctypes.byref(desc), _ptr(w), _ptr(w_scale), _ptr(w_zp), _ptr(out),
+                                                    _stream(w.device)))
+    return out if desc.num_experts else out.squeeze(0)
+
+
+def quant_input(inputs: torch.Tensor, dtype="float8e4m3"):
+    """Per-token dynamic quantization -> (q, fp32 scales (M, 1))."""
+    _require_cuda(inputs)
+    dt = dtypes.DataType.from_str(dtype)
+    if dt != dtypes.float8e4m3:
+        raise NotImplementedError(f"activation quantization to {dt} is not built")
+    x = inputs.reshape(-1, inputs.size(-1))
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    m, k = x.shape
+    q = torch.empty((m, k), dtype=torch.float8_e4m3fn, device=x.device)
+    scales = torch.empty((m, 1), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        native.check(native.lib.hm_quant_input(_ptr(x), _TORCH_TO_NATIVE[x.dtype], m, k, x.stride(0), dt.to_native(),
+                                               _ptr(q), _ptr(scales), _stream(x.device)))
+    return q.view(*inputs.shape), scales.view(*inputs.shape[:-1], 1)
+
+
+def gemm_plan(desc: native.GemmDesc, m: int) -> native.Plan:
+    plan = native.Plan()
+    native.check(native.lib.hm_gemm_plan(ctypes.byref(desc), m, ctypes.byref(plan)))
+    return plan
+
+
+def workspace_bytes(desc: native.GemmDesc, m: int) -> int:
+    return gemm_plan(desc, m).workspace_bytes
+
+
+def gemm(desc: native.GemmDesc, a: torch.Tensor, w, w_scale, w_zp, bias, c: torch.Tensor, workspace: torch.Tensor,
+         a_scale=None):
+    """Enqueue one dense GEMM on the current stream of ``a``'s device."""
+    _require_cuda(a, w, w_scale, w_zp, bias, c, workspace, a_scale)
+    m = a.size(0)
+    with torch.cuda.device(a.device):
+        native.check(native.lib.hm_gemm(
+            ctypes.byref(desc), m, _ptr(a), a.stride(0), _ptr(a_scale), _ptr(w), _ptr(w_scale), _ptr(w_zp), _ptr(bias),
+            _ptr(c), c.stride(0), _ptr(workspace), workspace.nelement() * workspace.element_size(),
+            _stream(a.device)))
+    return c
+
+
+def check_status(workspace: torch.Tensor):
+    """Synchronise and raise if a kernel using ``workspace`` aborted."""
+    with torch.cuda.device(workspace.device):
+        native.check(native.lib.hm_check_status(_ptr(workspace), workspace.nelement() * workspace.element_size(),
+                                                _stream(workspace.device)))

@@ -1,0 +1,122 @@
+"""Weight-side helpers with the reference's names (``humming/utils/weight.py``).
+
+``quantize_weight`` restates the arithmetic of the reference's quantizer kernel
+(``humming/include/humming/kernel/quant_weight.cuh:155-271``) with torch tensor
+ops -- it runs once at load time.  The ``prepare_humming_*`` functions are thin
+wrappers over the native repack entry points (``hm_repack_*``); the layout they
+produce is this library's own tile-interleaved layout, not the reference's
+fragment order, and is opaque to callers in both libraries.
+"""
+from typing import Optional
+
+import torch
+
+from humming_b200 import dtypes
+from humming_b200 import runtime
+
+
+def _group_view(weight: torch.Tensor, group_size: int) -> torch.Tensor:
+    e, n, k = weight.shape
+    return weight.reshape(e, n, k // group_size, group_size)
+
+
+def quantize_weight(
+    weight: torch.Tensor,
+    dtype: dtypes.DataType,
+    scale_dtype: Optional[dtypes.DataType],
+    group_size: int,
+    has_dynamic_zp: bool = False,
+    has_global_scale: bool = False,
+):
+    """float (N,K)/(E,N,K) -> (codes int32, scales, zero points, global scale).
+
+    Integer targets only (what the layer's on-the-fly path and the test
+    generators need here).  Same return convention as the reference
+    (``humming/utils/weight.py:9-100``): scales come back in ``scale_dtype``
+    (fp16/bf16) or fp32, zero points as int32 ``(…, N, K/g)``.
+    """
+    assert weight.dtype in (torch.float16, torch.bfloat16, torch.float32)
+    assert weight.ndim in (2, 3)
+    if has_global_scale:
+        raise NotImplementedError("global scale quantization is not built")
+    if not dtype.is_integer_type:
+        raise NotImplementedError(f"quantize_weight to {dtype} is not built (integer targets only)")
+    if dtype.is_signed:
+        raise ValueError("pass the unsigned counterpart of a signed integer dtype (as the reference's generators do)")
+    assert not has_dynamic_zp or scale_dtype is not None
+
+    squeeze = weight.ndim == 2
+    w = (weight.unsqueeze(0) if squeeze else weight).float()
+    e, n, k = w.shape
+    g = group_size if group_size > 0 else k
+    wg = _group_view(w, g)
+    half = float(2 ** (dtype.num_bits - 1))  # 8 for 4 bits
+    dmax = half - 1.0  # quant_weight.cuh:11-13
+    max_val = wg.amax(-1).clamp_min(1e-30)
+    min_val = wg.amin(-1).clamp_max(-1e-30)
+    if scale_dtype is None:
+        raise NotImplementedError("scale-free quantization is not built")
+
+    if not has_dynamic_zp:
+        # quant_weight.cuh:205-214: the larger-magnitude side is mapped to -2^(b-1).
+        max_abs = torch.maximum(max_val, min_val.abs())
+        min_abs = torch.minimum(max_val, min_val.abs())
+        scale = torch.maximum(max_abs / (dmax + 1.499), min_abs / (dmax + 0.499))
+        scale = torch.where(max_val > min_val.abs(), -scale, scale)
+        zero_point = None
+        inv = 1.0 / scale
+        q = torch.round(wg * inv.unsqueeze(-1)).to(torch.int32) + int(half)
+    else:
+        # quant_weight.cuh:215-219
+        scale = (max_val - min_val) / (dmax * 2 + 1)
+        zero_point = torch.round(-min_val / scale).to(torch.int32)
+        lo = zero_point.float() * -scale
+        inv = 1.0 / scale
+        q = torch.round((wg - lo.unsqueeze(-1)) * inv.unsqueeze(-1)).to(torch.int32)
+        q = q.clamp_(0, int(2 ** dtype.num_bits) - 1)
+    q = q.reshape(e, n, k)
+
+    if scale_dtype in (dtypes.float16, dtypes.bfloat16):
+        scale = scale.to(dtypes.torch_dtype_map[scale_dtype])
+    elif scale_dtype != dtypes.float32:
+        raise NotImplementedError(f"scale dtype {scale_dtype} is not built for integer targets")
+
+    if squeeze:
+        q = q.squeeze(0)
+        scale = scale.squeeze(0)
+        zero_point = zero_point.squeeze(0) if zero_point is not None else None
+    return q, scale, zero_point, None
+
+
+def prepare_humming_weight(weight: torch.Tensor, b_dtype, a_dtype, zero_point=None, packed: bool = False,
+                           padded_shape_n=None, padded_shape_k=None) -> torch.Tensor:
+    """(…, N, K) codes or (…, N, K*bits/32) packed -> prepared weight buffer
+    (reference ``humming/utils/weight.py:103-169``)."""
+    if padded_shape_n is not None or padded_shape_k is not None:
+        raise NotImplementedError("padded shapes are not built")
+    is_moe = weight.ndim == 3
+    w = weight if is_moe else weight.unsqueeze(0)
+    if not packed:
+        w = runtime.pack_weight(w.contiguous(), b_dtype.num_bits)
+    e, n, words = w.shape
+    k = words * 32 // b_dtype.num_bits
+    desc = runtime.make_desc(shape_n=n, shape_k=k, a_dtype=a_dtype, b_dtype=b_dtype, c_dtype=a_dtype,
+                             bs_dtype=a_dtype, group_size=0, num_experts=e if is_moe else 0)
+    out = runtime.repack_weight(desc, w.contiguous())
+    pk = 256 // a_dtype.num_bits
+    out = out.view(e, k // pk, n * pk * b_dtype.num_bits // 32)
+    return out if is_moe else out.squeeze(0)
+
+
+def prepare_humming_tensor_for_glu(tensor, shape_n: int, pad_shape_n: int = 0, is_moe: bool = False):
+    """Interleave the two halves of the N rows (second half first) so that the
+    pair a fused GLU epilogue combines sits in adjacent rows
+    (reference ``humming/utils/weight.py:225-239``, docs/CONFIG.md:100-102)."""
+    if tensor is None or tensor.nelement() == 0:
+        return tensor
+    t = tensor if is_moe else tensor.unsqueeze(0)
+    real_n = shape_n - pad_shape_n
+    idx = torch.arange(real_n, device=t.device).view(2, -1).flip(0).T.reshape(-1)
+    idx = torch.cat([idx, torch.arange(real_n, shape_n, device=t.device)])
+    t = t[:, idx].contiguous()
+    return t if is_moe else t.squeeze(0)

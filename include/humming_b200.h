@@ -1,0 +1,177 @@
+/*
+ * humming_b200 -- C ABI of the sm_100a quantized-GEMM path.
+ *
+ * Everything a binding needs is in this header: plain pointers, sizes and POD
+ * descriptors; no torch or C++ types.  All device pointers are caller-owned.
+ * Unless a comment says otherwise no entry point allocates device memory:
+ * scratch is passed in as `workspace` and sized with the matching
+ * *_workspace_bytes() query.  Work is enqueued on `stream` (a cudaStream_t
+ * passed as void*) and the call returns without synchronising.
+ *
+ * Return value: 0 on success, a negative HM_ERR_* code otherwise;
+ * hm_last_error() then returns a message for the calling thread.
+ *
+ * Each declaration names the interface of the reference implementation
+ * (inclusionAI/humming, paths relative to that project) that it replaces.
+ */
+#ifndef HUMMING_B200_H_
+#define HUMMING_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HM_API __attribute__((visibility("default")))
+
+enum {
+  HM_OK = 0,
+  HM_ERR_INVALID = -1,     /* bad shape / dtype / pointer / alignment          */
+  HM_ERR_UNSUPPORTED = -2, /* valid in the reference, not built here           */
+  HM_ERR_WORKSPACE = -3,   /* workspace missing or too small                   */
+  HM_ERR_CUDA = -4,        /* a CUDA runtime/driver call failed                */
+  HM_ERR_DEVICE = -5       /* the kernel reported an abort in its status words */
+};
+
+/* Data type codes.  Integers: HM_UINT(bits) / HM_INT(bits), 1..8 bits. */
+enum {
+  HM_F16 = 1,
+  HM_BF16 = 2,
+  HM_F32 = 3,
+  HM_E4M3 = 4,
+  HM_E5M2 = 5,
+  HM_E8M0 = 6,
+  HM_E2M1 = 7
+};
+#define HM_UINT(bits) (0x100 + (bits))
+#define HM_INT(bits) (0x200 + (bits))
+
+/* One quantized linear layer  C[M,N] = A[M,K] * dequant(W[N,K])^T  (+ bias).
+ * Mirrors the fields of HummingLayerMeta that select a kernel
+ * (humming/layer.py:21-40) plus the MoE options of the kernel front end
+ * (humming/kernel/humming.py:152-258, docs/CONFIG.md "MoE Config"). */
+typedef struct hm_gemm_desc {
+  int32_t shape_n;
+  int32_t shape_k;
+  int32_t a_dtype;      /* HM_F16 | HM_BF16 | HM_E4M3                               */
+  int32_t b_dtype;      /* HM_UINT(4) | HM_INT(4) | HM_E2M1 ...                     */
+  int32_t c_dtype;      /* HM_F16 | HM_BF16                                         */
+  int32_t bs_dtype;     /* HM_F16 | HM_BF16 | HM_F32 | HM_E8M0                      */
+  int32_t group_size;   /* weight-scale group along K; 0 = one scale per row        */
+  int32_t has_zp;       /* dynamic zero points (same groups as the scales)          */
+  int32_t has_bias;
+  int32_t num_experts;  /* 0 = dense layer                                          */
+  int32_t top_k;        /* MoE only                                                 */
+  int32_t is_moe_down;  /* MoE only: read row = id, multiply by topk weight         */
+  int32_t m_tile;       /* token tile override (16..256); 0 = choose from M         */
+  int32_t num_sms;      /* CTAs to launch at most; 0 = every SM of the device       */
+  int32_t flags;        /* HM_FLAG_*                                                */
+} hm_gemm_desc;
+
+/* Stage the dequantized weight tile in shared memory instead of tensor memory
+ * (slower; kept as a cross-check of the tensor-memory operand path). */
+#define HM_FLAG_A_OPERAND_SMEM 1
+/* Never split a tile's K range over several CTAs (batch-invariant results, the
+ * counterpart of use_stream_k=False, docs/CONFIG.md "Scheduler Config"). */
+#define HM_FLAG_NO_SPLIT_K 2
+
+/* Launch plan chosen for (desc, m); returned by hm_gemm_plan for tests,
+ * benchmarks and workspace sizing. */
+typedef struct hm_plan {
+  int32_t m_tile;         /* tokens per tile (UMMA N)                          */
+  int32_t n_tiles;        /* shape_n / 128                                     */
+  int32_t m_tiles;
+  int32_t kb_per_tile;    /* shape_k / 64                                      */
+  int32_t mode;           /* 0 = whole tiles round-robin, 1 = contiguous K-split */
+  int32_t grid;           /* CTAs launched                                     */
+  int32_t units_per_cta;  /* mode 1: (tile, k-block) units per CTA             */
+  int32_t reserved;
+  int64_t total_units;
+  int64_t workspace_bytes;
+} hm_plan;
+
+/* ---- load path ------------------------------------------------------------ */
+
+/* codes[numel] (one int32 per element, low `bits` bits used) -> little-endian
+ * bit stream, `bits` int32 words per 32 elements.  numel % 32 == 0.
+ * Replaces pack_weight_kernel<bits> (humming/include/humming/kernel/pack_weight.cuh:5-27, :52-72;
+ * wrapper humming/kernel/pack_weight.py:27-58). */
+HM_API int hm_pack_weight(const int32_t* codes, int32_t* packed, int64_t numel, int bits, void* stream);
+
+/* Inverse of hm_pack_weight.  Replaces unpack_weight_kernel<bits>
+ * (humming/include/humming/kernel/pack_weight.cuh:29-50, :75-95). */
+HM_API int hm_unpack_weight(const int32_t* packed, int32_t* codes, int64_t numel, int bits, void* stream);
+
+/* Packed K-major codes (E, N, K*bits/32) -> the tile-interleaved layout the GEMM
+ * streams: [expert][n_tile][k_block][half][row][16 B].  `out` must not alias
+ * `packed`.  Replaces prepare_humming_weight / weight_repack_nk
+ * (humming/utils/weight.py:103-169, humming/include/humming/kernel/process.cuh:102-259). */
+HM_API int hm_repack_weight(const hm_gemm_desc* desc, const int32_t* packed, int32_t* out, void* stream);
+
+/* Scales (E, N, K/g) in bs_dtype -> [expert][n_tile][group][128 rows].
+ * Replaces prepare_humming_weight_scale (humming/utils/weight.py:172-192). */
+HM_API int hm_repack_scale(const hm_gemm_desc* desc, const void* scales, void* out, void* stream);
+
+/* Zero points: 4-bit codes packed 8 per int32 in (E, N, K/g) element order ->
+ * [expert][n_tile][group][64 B] (row r in nibble r of the 64 bytes).
+ * Replaces prepare_humming_zero_point (humming/utils/weight.py:195-216). */
+HM_API int hm_repack_zero_point(const hm_gemm_desc* desc, const int32_t* zp, int32_t* out, void* stream);
+
+/* Prepared weight/scale/zero-point buffers -> dequantized weights (E, N, K) as
+ * fp32, computed with the same device function the GEMM uses (for 16-bit
+ * activations: rounded to a_dtype after the scale multiply, then widened).
+ * Test and debugging aid; the reference's counterpart is the `weight_ref`
+ * expression of humming/utils/test.py:109-128. */
+HM_API int hm_dequant_prepared(const hm_gemm_desc* desc, const void* w, const void* w_scale, const void* w_zp,
+                               float* out, void* stream);
+
+/* ---- forward path --------------------------------------------------------- */
+
+/* Per-token dynamic quantization of activations x[m,k] (row stride ldx elements,
+ * x_dtype HM_F16/HM_BF16/HM_F32) to q_dtype HM_E4M3: scale = max(absmax,1e-30)/448,
+ * q = rn_e4m3(x * (1/scale)); scales[m] fp32.
+ * Replaces torch.ops.humming.humming_quant_input with group_size=None
+ * (humming/kernel/quant_input.py:11-31, :91-199). */
+HM_API int hm_quant_input(const void* x, int x_dtype, int64_t m, int64_t k, int64_t ldx, int q_dtype, void* q,
+                          float* scales, void* stream);
+
+/* Launch plan (tile size, split, grid, workspace bytes) for `m` rows.
+ * Counterpart of the M-bucket table + scheduler constants
+ * (humming/layer.py:403-451, humming/include/humming/scheduler.cuh:55-99). */
+HM_API int hm_gemm_plan(const hm_gemm_desc* desc, int64_t m, hm_plan* plan);
+
+/* Bytes of zero-initialised workspace hm_gemm needs for `m` rows (0 on error).
+ * The kernel leaves the workspace's counters at zero again, so one buffer can
+ * be reused by successive launches on the same stream.  Replaces the `locks`
+ * buffer (humming/layer.py:154). */
+HM_API size_t hm_gemm_workspace_bytes(const hm_gemm_desc* desc, int64_t m);
+
+/* Dense GEMM.  a: (m, shape_k) a_dtype, row stride lda elements; a_scale: fp32
+ * per-token scales for 8-bit a_dtype else NULL; w / w_scale / w_zp: prepared
+ * buffers; bias: (shape_n) c_dtype or NULL; c: (m, shape_n) c_dtype, row stride
+ * ldc.  Replaces torch.ops.humming.launch_humming
+ * (humming/csrc/launcher/launcher.cpp:61-161) and the humming<> kernel
+ * (humming/include/humming/kernel/humming_ws.cuh:25-176). */
+HM_API int hm_gemm(const hm_gemm_desc* desc, int64_t m, const void* a, int64_t lda, const float* a_scale,
+                   const void* w, const void* w_scale, const void* w_zp, const void* bias, void* c, int64_t ldc,
+                   void* workspace, size_t workspace_bytes, void* stream);
+
+/* Reads the workspace's status words back (synchronises `stream`); returns
+ * HM_ERR_DEVICE and resets the workspace if the last kernels using it aborted. */
+HM_API int hm_check_status(void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- misc ----------------------------------------------------------------- */
+HM_API const char* hm_last_error(void);
+HM_API int hm_version(void);
+
+/* Host-side replay of the tile scheduler: fills out[] with up to `cap`
+ * segments (tile, kb_begin, kb_end, partial, nseg, first_cta, slot) x int32 of CTA
+ * `cta` under `plan`; returns the number of segments.  Used by the CPU tests. */
+HM_API int hm_debug_schedule(const hm_plan* plan, int cta, int32_t* out, int cap);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HUMMING_B200_H_ */

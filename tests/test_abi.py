@@ -1,0 +1,110 @@
+"""CPU checks of the C ABI: the library loads, exports every declared symbol,
+validates arguments, and its tile scheduler covers the work exactly once."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from humming_b200 import native
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "humming_b200.h")).read()
+    return sorted(set(re.findall(r"HM_API\s+[\w\s\*]+?\b(hm_\w+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported_and_bound():
+    names = _declared_symbols()
+    assert len(names) >= 14
+    for name in names:
+        assert hasattr(native.lib, name), f"{name} declared in the header but not exported"
+        assert name in native.SIGNATURES, f"{name} has no ctypes signature"
+    assert sorted(native.SIGNATURES) == names
+
+
+def _desc(**kw):
+    base = dict(shape_n=1024, shape_k=1024, a_dtype=1, b_dtype=0x104, c_dtype=1, bs_dtype=1, group_size=128, num_sms=148)
+    base.update(kw)
+    return native.GemmDesc(**base)
+
+
+def test_version_and_error_string():
+    assert native.lib.hm_version() >= 100
+    plan = native.Plan()
+    assert native.lib.hm_gemm_plan(_desc(shape_n=1000), 16, plan) == native.HM_ERR_INVALID
+    assert "128" in native.last_error()
+    assert native.lib.hm_gemm_plan(_desc(b_dtype=0x103), 16, plan) == native.HM_ERR_UNSUPPORTED
+    assert native.lib.hm_gemm_plan(_desc(a_dtype=4), 16, plan) == native.HM_ERR_UNSUPPORTED
+    assert native.lib.hm_gemm_plan(_desc(group_size=96), 16, plan) == native.HM_ERR_INVALID
+    assert native.lib.hm_gemm_plan(_desc(m_tile=48), 16, plan) == native.HM_ERR_INVALID
+    with pytest.raises(ValueError):
+        native.check(native.lib.hm_gemm_plan(_desc(shape_k=100), 16, plan))
+    with pytest.raises(NotImplementedError):
+        native.check(native.lib.hm_gemm_plan(_desc(bs_dtype=2), 16, plan))
+
+
+def test_null_pointers_are_rejected_without_touching_the_gpu():
+    d = _desc()
+    assert native.lib.hm_pack_weight(None, None, 1024, 4, None) == native.HM_ERR_INVALID
+    assert native.lib.hm_pack_weight(ctypes.c_void_p(16), ctypes.c_void_p(32), 1000, 4, None) == native.HM_ERR_INVALID
+    assert native.lib.hm_pack_weight(ctypes.c_void_p(16), ctypes.c_void_p(32), 1024, 9, None) == native.HM_ERR_INVALID
+    assert native.lib.hm_repack_weight(d, None, None, None) == native.HM_ERR_INVALID
+    assert native.lib.hm_gemm(d, 16, None, 1024, None, None, None, None, None, None, 1024, None, 0, None) == native.HM_ERR_INVALID
+    assert native.lib.hm_gemm(d, 0, None, 1024, None, None, None, None, None, None, 1024, None, 0, None) == native.HM_OK
+    assert native.lib.hm_quant_input(None, 2, 4, 64, 64, 4, None, None, None) == native.HM_ERR_INVALID
+
+
+def _segments(plan, cta):
+    cap = 4096
+    buf = (ctypes.c_int32 * (7 * cap))()
+    n = native.lib.hm_debug_schedule(plan, cta, buf, cap)
+    assert 0 <= n <= cap
+    return [tuple(buf[7 * i:7 * i + 7]) for i in range(n)]
+
+
+@pytest.mark.parametrize("n,k,m,flags", [
+    (1024, 1024, 16, 0), (28672, 4096, 1, 0), (28672, 4096, 64, 0), (4096, 14336, 16, 0), (4096, 4096, 256, 0),
+    (6144, 4096, 1024, 0), (28672, 4096, 8192, 0), (128, 128, 1, 0), (128, 128, 300, 0), (256, 384, 17, 0),
+    (4096, 4096, 16, native.HM_FLAG_NO_SPLIT_K), (1536, 2048, 77, 0),
+])
+def test_schedule_covers_every_unit_exactly_once(n, k, m, flags):
+    plan = native.Plan()
+    native.check(native.lib.hm_gemm_plan(_desc(shape_n=n, shape_k=k, flags=flags), m, plan))
+    tiles = plan.n_tiles * plan.m_tiles
+    kb = plan.kb_per_tile
+    assert plan.total_units == tiles * kb
+    assert 1 <= plan.grid <= 148
+    covered = {}
+    partial_by_tile = {}
+    slots = set()
+    for cta in range(plan.grid):
+        segs = _segments(plan, cta)
+        assert segs, "a launched CTA has no work"
+        n_partial = 0
+        for tile, kb0, kb1, partial, nseg, first_cta, slot in segs:
+            assert 0 <= tile < tiles and 0 <= kb0 < kb1 <= kb
+            assert partial == int(kb1 - kb0 < kb)
+            for u in range(tile * kb + kb0, tile * kb + kb1):
+                assert u not in covered
+                covered[u] = cta
+            if partial:
+                n_partial += 1
+                assert slot // 2 == cta and slot not in slots
+                slots.add(slot)
+                partial_by_tile.setdefault(tile, []).append((cta, nseg, first_cta, kb0, kb1))
+        assert n_partial <= 2
+    assert len(covered) == plan.total_units
+    if plan.mode == 0:
+        assert not partial_by_tile
+    for tile, parts in partial_by_tile.items():
+        ctas = sorted(p[0] for p in parts)
+        nseg, first = parts[0][1], parts[0][2]
+        assert all(p[1] == nseg and p[2] == first for p in parts)
+        assert ctas == list(range(first, first + nseg)), "contributors must be consecutive CTAs"
+    # workspace is big enough for every slot
+    if plan.mode == 1:
+        need = 256 + ((tiles * 16 + 255) // 256) * 256 + plan.grid * 2 * plan.m_tile * 128 * 4
+        assert plan.workspace_bytes >= need

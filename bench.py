@@ -1,0 +1,365 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-GEMM hot path on B200.
+
+Workload (BASELINE.json configs[1]): Llama-3-8B-shaped dense projections,
+W4A16 bf16, uint4 weights with dynamic zero points and bf16 group-128 scales;
+N x K in {6144x4096, 4096x4096, 28672x4096, 4096x14336}; M sweep
+1, 16, 64, 256, 1024, 4096, 8192.  One *step* is one pass over the whole sweep
+(4 projections x 7 values of M = 28 GEMMs) on seeded synthetic tensors.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line.  `value` is whole-job TFLOP/s (sum of 2*M*N*K over the
+sweep / step time) with inputs resident in HBM; `e2e` is the same metric through
+HummingLayer.forward with pinned host buffers and the H2D/D2H copies inside
+the timed region; `roofline` describes the dominant kernel (the 256-token-tile
+instantiation, tensor-bound) and `roofline_decode` the M <= 16 launches
+(HBM-bound); `cpu_baseline` times the oracle (fp32 dequant + torch.matmul) on
+the host cores over a bounded sample.  Dense layers do not shard: with
+--gpus N every rank runs an independent replica of the sweep ("replicas only").
+
+`--impl reference` times the reference's CPU path (the oracle port) instead.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+M_SWEEP = (1, 16, 64, 256, 1024, 4096, 8192)
+GROUP = 128
+METRIC = "W4A16 GEMM throughput, Llama-3-8B projection sweep (bf16 x uint4+zp, g128)"
+UNIT = "TFLOP/s"
+N_COPIES = 3  # weight copies rotated so the working set exceeds 2x L2 (3 x 109 MB)
+
+
+def shapes():
+    from humming_b200.utils import synthetic
+    return list(synthetic.LLAMA3_8B_SHAPES.items())
+
+
+def gemm_flops(m, n, k):
+    return 2.0 * m * n * k
+
+
+def gemm_bytes(m, n, k):
+    """Algorithmic bytes of one GEMM: codes + scales + zero points + activations + output."""
+    return n * k / 2 + n * (k // GROUP) * 2 + n * (k // GROUP) * 0.5 + m * k * 2 + m * n * 2
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_reference_sample(sample_ms=(16, 256), threads=None, repeat=1):
+    """The reference's CPU path on a bounded sample of the workload: for each of
+    the four projections dequantise to fp32 ((q - zp) * s, timed) and run
+    torch.matmul for each M of `sample_ms`.  Returns (tflops, seconds, cores, text)."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import humming_oracle as oracle
+    from humming_b200.utils import synthetic
+
+    cores = threads or os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    flops = 0.0
+    secs = 0.0
+    for _ in range(repeat):
+        for _name, (n, k) in shapes():
+            case = synthetic.dense_w4a16_case(n, k, torch.bfloat16, True, seed=0)
+            xs = [synthetic.activations(m, k, torch.bfloat16).float() for m in sample_ms]
+            t0 = time.perf_counter()
+            w = case.weight_ref()  # fp32 dequant, torch CPU (reference humming/utils/test.py:109-128)
+            for m, x in zip(sample_ms, xs):
+                oracle.gemm_ref(x, w, torch.bfloat16)
+                flops += gemm_flops(m, n, k)
+            secs += time.perf_counter() - t0
+            del w, case
+    text = f"4 projections x M in {list(sample_ms)}: fp32 dequant + torch.matmul per projection, {repeat} pass(es)"
+    return flops / secs / 1e12, secs, cores, text
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    steps = max(args.steps, 1)
+    sample = (16, 256)
+    for _ in range(min(args.warmup, 1)):
+        cpu_reference_sample(sample_ms=(16,))
+    t0 = time.perf_counter()
+    tf, secs, cores, text = cpu_reference_sample(sample_ms=sample, repeat=steps)
+    wall = time.perf_counter() - t0
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tf, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": min(args.warmup, 1), "ms_per_step": wall * 1e3 / steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "llama3-8b projections W4A16 bf16 (CPU oracle, bounded sample)", "shapes_nk": [list(s[1]) for s in shapes()],
+                   "m_sample": list(sample), "group_size": GROUP},
+        "cpu_baseline": {"value": tf, "unit": UNIT, "cores": cores, "kind": "port", "sample": text},
+        "e2e": {"value": tf, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch.distributed as dist
+    from humming_b200 import runtime
+    from humming_b200.layer import HummingLayer, HummingMethod
+    from humming_b200.utils import synthetic
+
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    peaks = measured_peaks()
+
+    # ---- build layers (N_COPIES rotating copies of each projection)
+    layers = {}
+    for name, (n, k) in shapes():
+        case = synthetic.dense_w4a16_case(n, k, torch.bfloat16, True, seed=0)
+        copies = []
+        for _ in range(N_COPIES):
+            layer = HummingLayer(shape_n=n, shape_k=k, a_dtype="bfloat16", b_dtype="uint4", c_dtype="bfloat16",
+                                 bs_dtype="bfloat16", weight_scale_group_size=GROUP, has_dynamic_zp=True).to(dev)
+            layer.load_weight(weight=case.codes.to(dev), weight_scale=case.scales.to(dev), zero_point=case.zero_points.to(dev))
+            layer.finish_load()
+            copies.append(layer)
+        layers[name] = copies
+        del case
+    ks = sorted({k for _, (_, k) in shapes()})
+    x_host = {(m, k): synthetic.activations(m, k, torch.bfloat16, seed=1 + rank).pin_memory() for m in M_SWEEP for k in ks}
+    x_dev = {key: t.to(dev) for key, t in x_host.items()}
+    out_dev = {(name, m): torch.empty((m, n), dtype=torch.bfloat16, device=dev) for name, (n, _) in shapes() for m in M_SWEEP}
+    points = [(mi, m, name, n, k) for mi, m in enumerate(M_SWEEP) for name, (n, k) in shapes()]
+    flops_step = sum(gemm_flops(m, n, k) for _, m, _, n, k in points)
+
+    def one_step():
+        for mi, m, name, n, k in points:
+            layers[name][mi % N_COPIES](inputs=x_dev[(m, k)], outputs=out_dev[(name, m)])
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        one_step()
+    torch.cuda.synchronize()
+    for copies in layers.values():
+        for layer in copies:
+            layer.check_status()
+
+    # ---- headline: K replays of the captured step
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        one_step()
+    graph.replay()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    time.sleep(0.3)
+    sync_all()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        graph.replay()
+    ev1.record()
+    sync_all()
+    ms_total = ev0.elapsed_time(ev1)
+    time.sleep(0.2)
+    clocks = sampler.stop()
+    ms_step = ms_total / args.steps
+
+    # ---- per-point launch durations (each point: one graph of REP launches over rotating copies)
+    per_point = []
+    REP = 6
+    for mi, m, name, n, k in points:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for r in range(REP):
+                layers[name][r % N_COPIES](inputs=x_dev[(m, k)], outputs=out_dev[(name, m)])
+        g.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        nrep = max(2, min(args.steps, 10))
+        a.record()
+        for _ in range(nrep):
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) * 1e3 / (nrep * REP)
+        plan = runtime.gemm_plan(HummingMethod._desc(layers[name][0].meta), m)
+        per_point.append({"proj": name, "m": m, "n": n, "k": k, "us": round(us, 2), "m_tile": plan.m_tile,
+                          "tflops": round(gemm_flops(m, n, k) / us / 1e6, 2), "gbs": round(gemm_bytes(m, n, k) / us / 1e3, 1)})
+        del g
+
+    # ---- e2e: public API, pinned host buffers, copies inside the timed region
+    out_host = {key: torch.empty(t.shape, dtype=t.dtype).pin_memory() for key, t in out_dev.items()}
+    e2e_steps = max(1, min(args.steps, 5))
+    h2d = sum(x_host[(m, k)].numel() * 2 for _, m, _, _, k in points)
+    d2h = sum(out_host[(name, m)].numel() * 2 for _, m, name, _, _ in points)
+
+    def e2e_step():
+        for mi, m, name, n, k in points:
+            xd = x_host[(m, k)].to(dev, non_blocking=True)
+            y = layers[name][mi % N_COPIES](inputs=xd, outputs=out_dev[(name, m)])
+            out_host[(name, m)].copy_(y, non_blocking=True)
+        torch.cuda.synchronize()
+
+    e2e_step()
+    sync_all()
+    t0 = time.perf_counter()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    sync_all()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    _ = time.perf_counter() - t0
+
+    # ---- reduce over ranks (max time)
+    t = torch.tensor([ms_step, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step, e2e_ms = float(t[0]), float(t[1])
+    if rank != 0:
+        return
+
+    value = world * flops_step / (ms_step * 1e-3) / 1e12
+    e2e_value = world * flops_step / (e2e_ms * 1e-3) / 1e12
+
+    big = [p for p in per_point if p["m_tile"] == 256]
+    big_flops = sum(gemm_flops(p["m"], p["n"], p["k"]) for p in big)
+    big_us = sum(p["us"] for p in big)
+    big_ach = big_flops / big_us / 1e6
+    top = max(per_point, key=lambda p: p["us"])
+    small = [p for p in per_point if p["m"] <= 16]
+    small_bytes = sum(gemm_bytes(p["m"], p["n"], p["k"]) for p in small)
+    small_us = sum(p["us"] for p in small)
+    small_ach = small_bytes / small_us / 1e3
+    peak_tc = peaks["bf16_tflops_sustained"]
+
+    cpu = None
+    if not args.no_cpu_baseline:
+        tf, secs, cores, text = cpu_reference_sample()
+        cpu = {"value": tf, "unit": UNIT, "cores": cores, "kind": "port", "sample": text, "seconds": round(secs, 2)}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": "llama3-8b projections W4A16 bf16: 4 shapes x M sweep = 28 GEMMs per step",
+                   "shapes_nk": [list(s[1]) for s in shapes()], "m_sweep": list(M_SWEEP), "group_size": GROUP,
+                   "weights": "uint4 + dynamic zero point, bf16 scales", "parallelism": "replicas only" if world > 1 else "single GPU",
+                   "l2": f"{N_COPIES} rotating weight copies per projection (327 MB of weights > 2x L2), weights loaded evict-first",
+                   "timing": "CUDA graph of one step replayed K times, CUDA events, max over ranks"},
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": e2e_ms, "steps": e2e_steps},
+        "gpu_launches": len(points) * args.steps,
+        "clocks": clocks,
+        "roofline": {"bound": "tensor", "achieved": big_ach, "peak": peak_tc, "unit": "TFLOP/s", "frac": big_ach / peak_tc,
+                     "traffic": None, "kernel": "gemm_w4a16_kernel<256,bf16,zp,tmem> (all launches with M >= 256)",
+                     "peak_source": f"{peaks['source']} cuBLAS bf16, sustained", "top_launch": top},
+        "roofline_decode": {"bound": "hbm", "achieved": small_ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                            "frac": small_ach / peaks["hbm_gbs"], "traffic": None,
+                            "kernel": "gemm_w4a16_kernel<16,bf16,zp,tmem> (all launches with M <= 16)",
+                            "peak_source": f"{peaks['source']} copy bandwidth"},
+        "cpu_baseline": cpu,
+        "sweep": per_point,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_ours(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -154,7 +154,7 @@ int launch_gemm(const hm::GemmParams& p, const CUtensorMap& tmap, int grid, cuda
     HM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_ALLOC));
     configured[dev & 63] = true;
   }
-  kern<<<grid, hm::kThreads, Cfg::SMEM_ALLOC, stream>>>(p, tmap);
+  kern<<<grid, Cfg::THREADS, Cfg::SMEM_ALLOC, stream>>>(p, tmap);
   HM_CUDA_OK(cudaGetLastError());
   return HM_OK;
 }

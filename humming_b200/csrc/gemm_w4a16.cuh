@@ -39,8 +39,7 @@ constexpr int kCodeBytes = kTileN * kBlockK / 2;  // 4096: packed 4-bit codes of
 constexpr int kScaleBytes = kTileN * 2;           // 256: one 16-bit scale per row
 constexpr int kZpBytes = kTileN / 2;              // 64: one nibble per row
 constexpr int kWStageBytes = 4480;                // 4096 + 256 + 64, padded to a multiple of 128
-constexpr int kThreads = 512;
-constexpr int kNumBarrierSlots = 96;
+constexpr int kNumBarrierSlots = 128;
 
 struct GemmParams {
   const uint8_t* w;        // prepared codes   [n_tile][kb][2][128][16 B]
@@ -60,24 +59,32 @@ struct GemmParams {
 
 template <int MT, bool A_TMEM>
 struct GemmCfg {
-  // Activation / operand-slot ring depth and packed-weight ring depth.
-  static constexpr int S = !A_TMEM ? 3 : (MT <= 128 ? 6 : 4);
+  // Ring depths: SX activation stages (shared memory; deep for small token
+  // tiles, where the stage is tiny and L2 latency must be covered), SA operand
+  // slots for the dequantized weights (tensor memory, 32 columns each, or 16 KB
+  // of shared memory in the cross-check variant), SW packed-weight stages.
+  static constexpr int SX = MT <= 16 ? 32 : MT <= 32 ? 24 : MT <= 64 ? 12 : MT <= 128 ? 6 : 4;
+  static constexpr int SA = A_TMEM ? 8 : 3;
   static constexpr int SW = MT <= 32 ? 16 : (MT <= 64 ? 12 : 8);
-  static constexpr int ACC_BUFS = (2 * MT + (A_TMEM ? S * 32 : 0) <= 512) ? 2 : 1;
+  // Dequant warp groups (4 warps each) taking k-blocks round-robin.
+  static constexpr int NGROUPS = MT <= 64 ? 4 : 2;
+  static constexpr int EPI_WARP0 = 4 + 4 * NGROUPS;
+  static constexpr int THREADS = (EPI_WARP0 + 4) * 32;
+  static constexpr int ACC_BUFS = (2 * MT + (A_TMEM ? SA * 32 : 0) <= 512) ? 2 : 1;
   static constexpr int A_COL0 = ACC_BUFS * MT;
-  static constexpr int USED_COLS = A_COL0 + (A_TMEM ? S * 32 : 0);
+  static constexpr int USED_COLS = A_COL0 + (A_TMEM ? SA * 32 : 0);
   static constexpr int TMEM_COLS = USED_COLS <= 32 ? 32 : USED_COLS <= 64 ? 64 : USED_COLS <= 128 ? 128 : USED_COLS <= 256 ? 256 : 512;
   static constexpr int X_STAGE = MT * 128;
   static constexpr int A_STAGE = A_TMEM ? 0 : kTileN * 128;
   static constexpr int SMEM_X = 0;
-  static constexpr int SMEM_A = SMEM_X + S * X_STAGE;
-  static constexpr int SMEM_W = SMEM_A + S * A_STAGE;
+  static constexpr int SMEM_A = SMEM_X + SX * X_STAGE;
+  static constexpr int SMEM_W = SMEM_A + SA * A_STAGE;
   static constexpr int SMEM_BAR = SMEM_W + SW * kWStageBytes;
   static constexpr int SMEM_TOTAL = SMEM_BAR + kNumBarrierSlots * 8 + 64;
   static constexpr int SMEM_ALLOC = SMEM_TOTAL + 1024;  // slack for manual 1024-byte alignment
   static_assert(USED_COLS <= 512, "tensor memory budget");
   static_assert(SMEM_ALLOC <= 232448, "shared memory budget");
-  static_assert(2 * SW + 3 * S + 5 <= kNumBarrierSlots, "barrier slots");
+  static_assert(2 * SW + 2 * SX + 2 * SA + 5 <= kNumBarrierSlots, "barrier slots");
 };
 
 template <bool BF16>
@@ -107,11 +114,13 @@ HM_DEVICE void report_abort(int* status, int code, int a, int b) {
 }
 
 template <int MT, bool BF16, bool HAS_ZP, bool A_TMEM>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(GemmCfg<MT, A_TMEM>::THREADS, 1)
 gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
   using Cfg = GemmCfg<MT, A_TMEM>;
-  constexpr int S = Cfg::S;
+  constexpr int SX = Cfg::SX;
+  constexpr int SA = Cfg::SA;
   constexpr int SW = Cfg::SW;
+  constexpr int NGROUPS = Cfg::NGROUPS;
   constexpr int ACC_BUFS = Cfg::ACC_BUFS;
 
   extern __shared__ uint8_t smem_raw[];
@@ -126,11 +135,13 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
   auto w_full = [&](int i) { return bar0 + 8u * i; };
   auto w_empty = [&](int i) { return bar0 + 8u * (SW + i); };
   auto x_full = [&](int i) { return bar0 + 8u * (2 * SW + i); };
-  auto a_full = [&](int i) { return bar0 + 8u * (2 * SW + S + i); };
-  auto consumed = [&](int i) { return bar0 + 8u * (2 * SW + 2 * S + i); };
-  auto acc_full = [&](int i) { return bar0 + 8u * (2 * SW + 3 * S + i); };
-  auto acc_empty = [&](int i) { return bar0 + 8u * (2 * SW + 3 * S + 2 + i); };
-  const uint32_t drain_bar = bar0 + 8u * (2 * SW + 3 * S + 4);
+  auto x_empty = [&](int i) { return bar0 + 8u * (2 * SW + SX + i); };
+  auto a_full = [&](int i) { return bar0 + 8u * (2 * SW + 2 * SX + i); };
+  auto a_empty = [&](int i) { return bar0 + 8u * (2 * SW + 2 * SX + SA + i); };
+  constexpr int kBarAcc = 2 * SW + 2 * SX + 2 * SA;
+  auto acc_full = [&](int i) { return bar0 + 8u * (kBarAcc + i); };
+  auto acc_empty = [&](int i) { return bar0 + 8u * (kBarAcc + 2 + i); };
+  const uint32_t drain_bar = bar0 + 8u * (kBarAcc + 4);
   volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem_gen + Cfg::SMEM_BAR + kNumBarrierSlots * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + Cfg::SMEM_BAR + kNumBarrierSlots * 8 + 8);
 
@@ -142,10 +153,13 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
       mbar_init(w_full(i), 1);
       mbar_init(w_empty(i), 4);
     }
-    for (int i = 0; i < S; ++i) {
+    for (int i = 0; i < SX; ++i) {
       mbar_init(x_full(i), 1);
+      mbar_init(x_empty(i), 1);
+    }
+    for (int i = 0; i < SA; ++i) {
       mbar_init(a_full(i), 4);
-      mbar_init(consumed(i), 1);
+      mbar_init(a_empty(i), 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(acc_full(i), 1);
@@ -213,9 +227,9 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
       bool ok = true;
       while (ok && iter.next(seg)) {
         for (int kb = seg.kb0; kb < seg.kb1; ++kb, ++it) {
-          const int s = it % S;
-          const uint32_t ph = (it / S) & 1;
-          if (!mbar_wait_bounded(consumed(s), ph ^ 1, abort_flag)) {
+          const int s = it % SX;
+          const uint32_t ph = (it / SX) & 1;
+          if (!mbar_wait_bounded(x_empty(s), ph ^ 1, abort_flag)) {
             report_abort(p.status, HM_ABORT_X_EMPTY, it, s);
             ok = false;
             break;
@@ -225,9 +239,9 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
         }
       }
       if (!ok) {
-        for (int j = 0; j < S && j < it; ++j) {
+        for (int j = 0; j < SX && j < it; ++j) {
           const int last_it = it - 1 - j;
-          mbar_wait_bounded(x_full(last_it % S), (last_it / S) & 1, abort_flag + 1);
+          mbar_wait_bounded(x_full(last_it % SX), (last_it / SX) & 1, abort_flag + 1);
         }
       }
     }
@@ -249,26 +263,28 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + b * MT;
         for (int kb = seg.kb0; kb < seg.kb1; ++kb, ++it) {
-          const int s = it % S;
-          const uint32_t ph = (it / S) & 1;
-          if (!mbar_wait_bounded(a_full(s), ph, abort_flag) || !mbar_wait_bounded(x_full(s), ph, abort_flag)) {
-            report_abort(p.status, HM_ABORT_MMA_OPERANDS, it, s);
+          const int sx = it % SX;
+          const int sa = it % SA;
+          if (!mbar_wait_bounded(a_full(sa), (it / SA) & 1, abort_flag) ||
+              !mbar_wait_bounded(x_full(sx), (it / SX) & 1, abort_flag)) {
+            report_abort(p.status, HM_ABORT_MMA_OPERANDS, it, sa);
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t xs = x_smem + s * Cfg::X_STAGE;
+          const uint32_t xs = x_smem + sx * Cfg::X_STAGE;
 #pragma unroll
           for (int k4 = 0; k4 < kBlockK / 16; ++k4) {
             const uint32_t accumulate = (kb != seg.kb0 || k4 != 0) ? 1u : 0u;
             const uint64_t b_desc = umma_desc_sw128(xs, k4 * 32);
             if constexpr (A_TMEM) {
-              mma_f16_ts(d_tmem, tmem_base + Cfg::A_COL0 + s * 32 + k4 * 8, b_desc, idesc, accumulate);
+              mma_f16_ts(d_tmem, tmem_base + Cfg::A_COL0 + sa * 32 + k4 * 8, b_desc, idesc, accumulate);
             } else {
-              mma_f16_ss(d_tmem, umma_desc_sw128(a_smem + s * Cfg::A_STAGE, k4 * 32), b_desc, idesc, accumulate);
+              mma_f16_ss(d_tmem, umma_desc_sw128(a_smem + sa * Cfg::A_STAGE, k4 * 32), b_desc, idesc, accumulate);
             }
           }
-          tc_commit(consumed(s));
+          tc_commit(x_empty(sx));
+          tc_commit(a_empty(sa));
         }
         if (!ok) break;
         tc_commit(acc_full(b));
@@ -280,18 +296,18 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
         mbar_wait_bounded(drain_bar, 0, abort_flag + 1);
       }
     }
-  } else if (warp >= 4 && warp < 12) {
+  } else if (warp >= 4 && warp < Cfg::EPI_WARP0) {
     // ------------------------------------------------ dequant warps
-    const int group = (warp - 4) >> 2;  // alternates k-blocks with the other group
+    const int group = (warp - 4) >> 2;  // groups take k-blocks round-robin
     const int q = warp & 3;             // TMEM lane quarter this warp may access
     const int row = q * 32 + lane;
     int it = 0;
     bool ok = true;
     while (ok && iter.next(seg)) {
       for (int kb = seg.kb0; kb < seg.kb1; ++kb, ++it) {
-        if ((it & 1) != group) continue;
+        if ((it % NGROUPS) != group) continue;
         const int sw = it % SW;
-        const int s = it % S;
+        const int s = it % SA;
         if (!mbar_wait_bounded(w_full(sw), (it / SW) & 1, abort_flag)) {
           if (lane == 0) report_abort(p.status, HM_ABORT_DQ_W_FULL, it, sw);
           ok = false;
@@ -320,7 +336,7 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
         __syncwarp();
         if (lane == 0) mbar_arrive(w_empty(sw));
         // Wait until the MMAs that read this operand slot last time are done.
-        if (!mbar_wait_bounded(consumed(s), ((it / S) & 1) ^ 1, abort_flag)) {
+        if (!mbar_wait_bounded(a_empty(s), ((it / SA) & 1) ^ 1, abort_flag)) {
           if (lane == 0) report_abort(p.status, HM_ABORT_DQ_SLOT, it, s);
           ok = false;
           break;
@@ -344,7 +360,7 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
         if (lane == 0) mbar_arrive(a_full(s));
       }
     }
-  } else if (warp >= 12) {
+  } else if (warp >= Cfg::EPI_WARP0) {
     // ------------------------------------------------ epilogue warps
     const int q = warp & 3;
     const int row = q * 32 + lane;
@@ -405,14 +421,27 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
         last = __shfl_sync(0xffffffffu, last, 0);
         if (last) {
           __threadfence();
-          for (int j = 0; j < m_valid; ++j) {
-            float acc = 0.f;
+          // Sum the contributors in CTA order (a fixed order, so the result does
+          // not depend on who arrived last); 8 columns at a time keeps 8 loads per
+          // contributor in flight.
+          for (int j0 = 0; j0 < m_valid; j0 += 8) {
+            float acc[8];
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) acc[jj] = 0.f;
             for (int cs = 0; cs < seg.nseg; ++cs) {
               const int cta = seg.first_cta + cs;
-              const float* src = p.partials + static_cast<size_t>(sched_slot(p.sched, cta, seg.tile)) * (MT * kTileN);
-              acc += __ldcg(src + j * kTileN + row);
+              const float* src = p.partials + static_cast<size_t>(sched_slot(p.sched, cta, seg.tile)) * (MT * kTileN) +
+                                 j0 * kTileN + row;
+              float v[8];
+#pragma unroll
+              for (int jj = 0; jj < 8; ++jj) v[jj] = (j0 + jj < m_valid) ? __ldcg(src + jj * kTileN) : 0.f;
+#pragma unroll
+              for (int jj = 0; jj < 8; ++jj) acc[jj] += v[jj];
             }
-            store_out<BF16>(p.c, static_cast<size_t>(m0 + j) * p.ldc + n, acc + bias);
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) {
+              if (j0 + jj < m_valid) store_out<BF16>(p.c, static_cast<size_t>(m0 + j0 + jj) * p.ldc + n, acc[jj] + bias);
+            }
           }
         }
       }

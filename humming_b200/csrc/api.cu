@@ -17,6 +17,8 @@
 namespace {
 
 thread_local char g_err[512] = "";
+unsigned long long* g_trace = nullptr;  // set by hm_debug_set_trace
+int g_dbg = 0;
 
 int fail(int code, const char* fmt, ...) {
   va_list ap;
@@ -312,6 +314,12 @@ size_t hm_gemm_workspace_bytes(const hm_gemm_desc* desc, int64_t m) {
   return static_cast<size_t>(pl.workspace_bytes);
 }
 
+int hm_debug_set_trace(void* device_buffer, int experiment_flags) {
+  g_trace = static_cast<unsigned long long*>(device_buffer);
+  g_dbg = experiment_flags;
+  return HM_OK;
+}
+
 int hm_debug_schedule(const hm_plan* plan, int cta, int32_t* out, int cap) {
   if (plan == nullptr || out == nullptr) return fail(HM_ERR_INVALID, "NULL pointer");
   hm::SegIter it;
@@ -380,6 +388,8 @@ int hm_gemm(const hm_gemm_desc* desc, int64_t m, const void* a, int64_t lda, con
   p.groups = desc->shape_k / g;
   p.kb_per_group = g / hm::kBlockK;
   p.sched = sched_of(pl);
+  p.trace = g_trace;
+  p.dbg = g_dbg;
 
   const bool a_tmem = !(desc->flags & HM_FLAG_A_OPERAND_SMEM);
   auto s = static_cast<cudaStream_t>(stream);

@@ -40,6 +40,9 @@ constexpr int kScaleBytes = kTileN * 2;           // 256: one 16-bit scale per r
 constexpr int kZpBytes = kTileN / 2;              // 64: one nibble per row
 constexpr int kWStageBytes = 4480;                // 4096 + 256 + 64, padded to a multiple of 128
 constexpr int kNumBarrierSlots = 128;
+constexpr int kTraceEvents = 128;  // traced k-blocks per role
+// Timing experiments (results become wrong; used only to locate bottlenecks).
+enum : int { HM_DBG_SKIP_MATH = 1, HM_DBG_SKIP_TMEM_ST = 2, HM_DBG_SKIP_MMA = 4, HM_DBG_SKIP_X_LOAD = 8, HM_DBG_SKIP_W_LOAD = 16 };
 
 struct GemmParams {
   const uint8_t* w;        // prepared codes   [n_tile][kb][2][128][16 B]
@@ -55,6 +58,8 @@ struct GemmParams {
   int groups;              // scale groups along K
   int kb_per_group;        // k-blocks per scale group
   SchedParams sched;
+  unsigned long long* trace;  // debug: per-role clock64 timeline of CTA 0, or null
+  int dbg;                    // debug: HM_DBG_* experiment switches (0 in production)
 };
 
 template <int MT, bool A_TMEM>
@@ -184,6 +189,10 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
   SegIter iter;
   iter.init(p.sched, blockIdx.x);
   Segment seg;
+  const bool tracing = p.trace != nullptr && blockIdx.x == 0;
+  auto trace = [&](int role, int idx, int j) {
+    if (tracing && idx < kTraceEvents) p.trace[(role * kTraceEvents + idx) * 4 + j] = clock64();
+  };
 
   if (warp == 0) {
     // ------------------------------------------------ weight producer
@@ -202,14 +211,20 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
             ok = false;
             break;
           }
+          trace(0, it, 0);
           const uint32_t dst = w_smem + sw * kWStageBytes;
           const int g = kb / p.kb_per_group;
-          mbar_arrive_expect_tx(w_full(sw), kCodeBytes + kScaleBytes + (HAS_ZP ? kZpBytes : 0));
-          bulk_g2s_hint(dst, p.w + (tile_code0 + kb) * kCodeBytes, kCodeBytes, w_full(sw), pol);
-          bulk_g2s(dst + kCodeBytes, p.w_scale + (tile_grp0 + g) * kScaleBytes, kScaleBytes, w_full(sw));
-          if constexpr (HAS_ZP) {
-            bulk_g2s(dst + kCodeBytes + kScaleBytes, p.w_zp + (tile_grp0 + g) * kZpBytes, kZpBytes, w_full(sw));
+          if (p.dbg & HM_DBG_SKIP_W_LOAD) {
+            mbar_arrive(w_full(sw));
+          } else {
+            mbar_arrive_expect_tx(w_full(sw), kCodeBytes + kScaleBytes + (HAS_ZP ? kZpBytes : 0));
+            bulk_g2s_hint(dst, p.w + (tile_code0 + kb) * kCodeBytes, kCodeBytes, w_full(sw), pol);
+            bulk_g2s(dst + kCodeBytes, p.w_scale + (tile_grp0 + g) * kScaleBytes, kScaleBytes, w_full(sw));
+            if constexpr (HAS_ZP) {
+              bulk_g2s(dst + kCodeBytes + kScaleBytes, p.w_zp + (tile_grp0 + g) * kZpBytes, kZpBytes, w_full(sw));
+            }
           }
+          trace(0, it, 1);
         }
       }
       if (!ok) {
@@ -234,8 +249,14 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(x_full(s), Cfg::X_STAGE);
-          tma_load_2d(x_smem + s * Cfg::X_STAGE, &tmap_x, kb * kBlockK, seg.m_tile * MT, x_full(s));
+          trace(1, it, 0);
+          if (p.dbg & HM_DBG_SKIP_X_LOAD) {
+            mbar_arrive(x_full(s));
+          } else {
+            mbar_arrive_expect_tx(x_full(s), Cfg::X_STAGE);
+            tma_load_2d(x_smem + s * Cfg::X_STAGE, &tmap_x, kb * kBlockK, seg.m_tile * MT, x_full(s));
+          }
+          trace(1, it, 1);
         }
       }
       if (!ok) {
@@ -265,16 +286,20 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
         for (int kb = seg.kb0; kb < seg.kb1; ++kb, ++it) {
           const int sx = it % SX;
           const int sa = it % SA;
-          if (!mbar_wait_bounded(a_full(sa), (it / SA) & 1, abort_flag) ||
-              !mbar_wait_bounded(x_full(sx), (it / SX) & 1, abort_flag)) {
+          trace(2, it, 0);
+          const bool a_ok = mbar_wait_bounded(a_full(sa), (it / SA) & 1, abort_flag);
+          trace(2, it, 1);
+          if (!a_ok || !mbar_wait_bounded(x_full(sx), (it / SX) & 1, abort_flag)) {
             report_abort(p.status, HM_ABORT_MMA_OPERANDS, it, sa);
             ok = false;
             break;
           }
+          trace(2, it, 2);
           tc_fence_after();
           const uint32_t xs = x_smem + sx * Cfg::X_STAGE;
 #pragma unroll
           for (int k4 = 0; k4 < kBlockK / 16; ++k4) {
+            if (p.dbg & HM_DBG_SKIP_MMA) break;
             const uint32_t accumulate = (kb != seg.kb0 || k4 != 0) ? 1u : 0u;
             const uint64_t b_desc = umma_desc_sw128(xs, k4 * 32);
             if constexpr (A_TMEM) {
@@ -285,6 +310,7 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
           }
           tc_commit(x_empty(sx));
           tc_commit(a_empty(sa));
+          trace(2, it, 3);
         }
         if (!ok) break;
         tc_commit(acc_full(b));
@@ -313,6 +339,7 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
           ok = false;
           break;
         }
+        if (q == 0 && lane == 0) trace(3 + group, it, 0);
         const uint8_t* ws = smem_gen + Cfg::SMEM_W + sw * kWStageBytes;
         const uint4 lo = *reinterpret_cast<const uint4*>(ws + row * 16);
         const uint4 hi = *reinterpret_cast<const uint4*>(ws + 2048 + row * 16);
@@ -324,6 +351,10 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
         }
         const uint32_t zpm = zp_magic_pair<BF16>(zp);
         uint32_t out[32];
+        if (p.dbg & HM_DBG_SKIP_MATH) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) out[i] = lo.x + i;
+        } else {
         dequant_word_u4<BF16>(lo.x, zpm, scale2, out + 0);
         dequant_word_u4<BF16>(lo.y, zpm, scale2, out + 4);
         dequant_word_u4<BF16>(lo.z, zpm, scale2, out + 8);
@@ -332,19 +363,26 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
         dequant_word_u4<BF16>(hi.y, zpm, scale2, out + 20);
         dequant_word_u4<BF16>(hi.z, zpm, scale2, out + 24);
         dequant_word_u4<BF16>(hi.w, zpm, scale2, out + 28);
+        }
         // The packed stage has been consumed into registers: hand it back.
         __syncwarp();
         if (lane == 0) mbar_arrive(w_empty(sw));
+        if (q == 0 && lane == 0) trace(3 + group, it, 1);
         // Wait until the MMAs that read this operand slot last time are done.
         if (!mbar_wait_bounded(a_empty(s), ((it / SA) & 1) ^ 1, abort_flag)) {
           if (lane == 0) report_abort(p.status, HM_ABORT_DQ_SLOT, it, s);
           ok = false;
           break;
         }
+        if (q == 0 && lane == 0) trace(3 + group, it, 2);
         if constexpr (A_TMEM) {
           tc_fence_after();
-          tmem_st_x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + Cfg::A_COL0 + s * 32, out);
-          tc_wait_st();
+          if (!(p.dbg & HM_DBG_SKIP_TMEM_ST)) {
+            tmem_st_x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + Cfg::A_COL0 + s * 32, out);
+            tc_wait_st();
+          } else if (out[5] == 0x12345u) {
+            p.status[7] = out[9];  // keep the math alive when the store is skipped
+          }
           tc_fence_before();
         } else {
           // 128-byte rows, 16-byte chunk c of row r stored at chunk (c ^ (r & 7)).
@@ -358,6 +396,7 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(a_full(s));
+        if (q == 0 && lane == 0) trace(3 + group, it, 3);
       }
     }
   } else if (warp >= Cfg::EPI_WARP0) {

@@ -67,7 +67,7 @@ int validate_desc(const hm_gemm_desc* d) {
   if (d == nullptr) return fail(HM_ERR_INVALID, "desc is NULL");
   if (d->shape_n <= 0 || d->shape_k <= 0) return fail(HM_ERR_INVALID, "shape_n/shape_k must be positive");
   if (d->shape_n % hm::kTileN != 0) return fail(HM_ERR_INVALID, "shape_n=%d must be a multiple of 128", d->shape_n);
-  if (d->shape_k % hm::kBlockK != 0) return fail(HM_ERR_INVALID, "shape_k=%d must be a multiple of 64", d->shape_k);
+  if (d->shape_k % hm::kStageK != 0) return fail(HM_ERR_INVALID, "shape_k=%d must be a multiple of 128", d->shape_k);
   if (d->group_size < 0) return fail(HM_ERR_INVALID, "group_size must be >= 0");
   const int g = d->group_size == 0 ? d->shape_k : d->group_size;
   if (d->shape_k % g != 0) return fail(HM_ERR_INVALID, "shape_k=%d not divisible by group_size=%d", d->shape_k, g);
@@ -77,7 +77,7 @@ int validate_desc(const hm_gemm_desc* d) {
     if (d->b_dtype == HM_INT(4) && d->has_zp) return fail(HM_ERR_INVALID, "dynamic zero point needs an unsigned weight dtype");
     if (d->c_dtype != d->a_dtype) return fail(HM_ERR_UNSUPPORTED, "c_dtype must equal a_dtype for 16-bit activations");
     if (d->bs_dtype != d->a_dtype) return fail(HM_ERR_UNSUPPORTED, "bs_dtype must equal a_dtype for 16-bit activations");
-    if (g % hm::kBlockK != 0) return fail(HM_ERR_UNSUPPORTED, "group_size=%d must be a multiple of 64", g);
+    if (g != 64 && g % hm::kStageK != 0) return fail(HM_ERR_UNSUPPORTED, "group_size=%d must be 64 or a multiple of 128", g);
   } else {
     return fail(HM_ERR_UNSUPPORTED, "a_dtype code %d not built", d->a_dtype);
   }
@@ -102,7 +102,7 @@ int make_plan(const hm_gemm_desc* d, int64_t m, hm_plan* plan) {
   plan->m_tile = mt;
   plan->n_tiles = d->shape_n / hm::kTileN;
   plan->m_tiles = static_cast<int32_t>((m + mt - 1) / mt);
-  plan->kb_per_tile = d->shape_k / hm::kBlockK;
+  plan->kb_per_tile = d->shape_k / hm::kStageK;
   const int64_t tiles = static_cast<int64_t>(plan->n_tiles) * plan->m_tiles;
   const int64_t units = tiles * plan->kb_per_tile;
   if (units >= (1ll << 31)) return fail(HM_ERR_INVALID, "problem too large for 32-bit unit indices");
@@ -119,7 +119,7 @@ int make_plan(const hm_gemm_desc* d, int64_t m, hm_plan* plan) {
     plan->workspace_bytes = 256;
   } else {
     plan->mode = 1;
-    const int64_t min_units = 4;  // do not cut work finer than 4 k-blocks per CTA
+    const int64_t min_units = 2;  // do not cut work finer than two 128-K steps per CTA
     int64_t max_ctas = units / min_units;
     if (max_ctas < 1) max_ctas = 1;
     int64_t grid = max_ctas < sms ? max_ctas : sms;
@@ -386,7 +386,8 @@ int hm_gemm(const hm_gemm_desc* desc, int64_t m, const void* a, int64_t lda, con
   p.K = desc->shape_k;
   p.ldc = static_cast<int>(ldc);
   p.groups = desc->shape_k / g;
-  p.kb_per_group = g / hm::kBlockK;
+  p.steps_per_group = g >= hm::kStageK ? g / hm::kStageK : 1;
+  p.groups_per_step = g >= hm::kStageK ? 1 : hm::kStageK / g;
   p.sched = sched_of(pl);
   p.trace = g_trace;
   p.dbg = g_dbg;

@@ -6,18 +6,25 @@
 // decode (M = 1..64, HBM-bound) and prefill (M in the thousands, tensor-bound).
 //
 //   warp 0        weight producer: 1-D bulk copies of packed codes + group
-//                 scales (+ zero points) into a deep shared-memory ring
+//                 scales (+ zero points) for 128 K-elements per stage into a
+//                 shared-memory ring
 //   warp 1        activation producer: 2-D TMA boxes (64 K x m_tile rows,
-//                 128-byte swizzle) into a second ring
-//   warp 2        MMA issuer: tcgen05.mma kind::f16, fp32 accumulators in TMEM
+//                 128-byte swizzle) into a second, deeper ring
+//   warp 2        MMA issuer: tcgen05.mma kind::f16, fp32 accumulators in TMEM.
+//                 The whole warp runs the loop (uniform control flow, so
+//                 descriptors live in uniform registers); one lane issues.
 //   warp 3        TMEM allocation / release
-//   warps 4..11   dequant: thread = weight row; 32 bytes of codes -> 64 values
+//   warps 4..19   dequant: thread = weight row; 64 bytes of codes -> 128 values
 //                 of the activation type, written straight into tensor memory
 //                 (tcgen05.st) where the MMA reads them as its A operand --
-//                 the expanded weights never touch shared memory.  Two groups
-//                 of four warps alternate k-blocks.
-//   warps 12..15  epilogue: tcgen05.ld -> (+bias) -> cast -> global, or fp32
+//                 the expanded weights never touch shared memory.  Four groups
+//                 of four warps take stages round-robin.
+//   warps 20..23  epilogue: tcgen05.ld -> (+bias) -> cast -> global, or fp32
 //                 partials + last-arriver reduction when K is split
+//
+// The single-thread roles are latency-bound on their own instruction streams
+// (an mbarrier test costs ~100 cycles round trip), so a stage carries 128
+// K-elements and the loops avoid everything but increments.
 //
 // Replaces the reference's humming<> kernel
 // (humming/include/humming/kernel/humming_ws.cuh:25-176) and its pipelines
@@ -33,19 +40,23 @@
 
 namespace hm {
 
-constexpr int kTileN = 128;        // weight rows per tile (UMMA M)
-constexpr int kBlockK = 64;        // K elements per pipeline stage
-constexpr int kCodeBytes = kTileN * kBlockK / 2;  // 4096: packed 4-bit codes of one stage
-constexpr int kScaleBytes = kTileN * 2;           // 256: one 16-bit scale per row
-constexpr int kZpBytes = kTileN / 2;              // 64: one nibble per row
-constexpr int kWStageBytes = 4480;                // 4096 + 256 + 64, padded to a multiple of 128
+constexpr int kTileN = 128;   // weight rows per tile (UMMA M)
+constexpr int kBlockK = 64;   // K elements per activation box / per 4 KB block of prepared codes
+constexpr int kStageK = 128;  // K elements per weight stage / operand slot / scheduler unit
+constexpr int kCodeBytes = kTileN * kBlockK / 2;  // 4096: packed 4-bit codes of one 64-K block
+constexpr int kScaleBytes = kTileN * 2;           // 256: one 16-bit scale per row and group
+constexpr int kZpBytes = kTileN / 2;              // 64: one nibble per row and group
+// One weight stage: codes of two 64-K blocks, scales and zero points of up to two groups.
+constexpr int kWScaleOff = 2 * kCodeBytes;
+constexpr int kWZpOff = kWScaleOff + 2 * kScaleBytes;
+constexpr int kWStageBytes = kWZpOff + 2 * kZpBytes;  // 8832
 constexpr int kNumBarrierSlots = 128;
-constexpr int kTraceEvents = 128;  // traced k-blocks per role
+constexpr int kTraceEvents = 128;  // traced stages per role
 // Timing experiments (results become wrong; used only to locate bottlenecks).
 enum : int { HM_DBG_SKIP_MATH = 1, HM_DBG_SKIP_TMEM_ST = 2, HM_DBG_SKIP_MMA = 4, HM_DBG_SKIP_X_LOAD = 8, HM_DBG_SKIP_W_LOAD = 16 };
 
 struct GemmParams {
-  const uint8_t* w;        // prepared codes   [n_tile][kb][2][128][16 B]
+  const uint8_t* w;        // prepared codes   [n_tile][K/64][2][128][16 B]
   const uint8_t* w_scale;  // prepared scales  [n_tile][group][128] x 16 bit
   const uint8_t* w_zp;     // prepared zero points [n_tile][group][64 B] or null
   const void* bias;        // [N] in the output type, or null
@@ -56,31 +67,35 @@ struct GemmParams {
   int M, N, K;
   int ldc;
   int groups;              // scale groups along K
-  int kb_per_group;        // k-blocks per scale group
-  SchedParams sched;
+  int steps_per_group;     // 128-K steps per scale group (>= 1)
+  int groups_per_step;     // scale groups per 128-K step (1 or 2)
+  SchedParams sched;       // units are 128-K steps
   unsigned long long* trace;  // debug: per-role clock64 timeline of CTA 0, or null
   int dbg;                    // debug: HM_DBG_* experiment switches (0 in production)
 };
 
 template <int MT, bool A_TMEM>
 struct GemmCfg {
-  // Ring depths: SX activation stages (shared memory; deep for small token
-  // tiles, where the stage is tiny and L2 latency must be covered), SA operand
-  // slots for the dequantized weights (tensor memory, 32 columns each, or 16 KB
-  // of shared memory in the cross-check variant), SW packed-weight stages.
-  static constexpr int SX = MT <= 16 ? 32 : MT <= 32 ? 24 : MT <= 64 ? 12 : MT <= 128 ? 6 : 4;
-  static constexpr int SA = A_TMEM ? 8 : 3;
-  static constexpr int SW = MT <= 32 ? 16 : (MT <= 64 ? 12 : 8);
-  // Dequant warp groups (4 warps each) taking k-blocks round-robin.
-  static constexpr int NGROUPS = MT <= 64 ? 4 : 2;
+  // Ring depths: SX activation boxes (64 K each, shared memory; deep for small
+  // token tiles where a box is tiny and L2 latency must be covered), SA operand
+  // slots for the dequantized weights (128 K each: 64 TMEM columns, or 32 KB of
+  // shared memory in the cross-check variant), SW packed-weight stages (128 K).
+  static constexpr int SX = !A_TMEM ? (MT <= 32 ? 8 : MT <= 128 ? 4 : 2)
+                                    : (MT <= 16 ? 24 : MT <= 32 ? 16 : MT <= 64 ? 12 : MT <= 128 ? 6 : 4);
+  static constexpr int SA = A_TMEM ? 4 : 2;
+  static constexpr int SW = MT <= 64 ? 8 : 4;
+  // Dequant warp groups (4 warps each) taking stages round-robin.
+  static constexpr int NGROUPS = 4;
   static constexpr int EPI_WARP0 = 4 + 4 * NGROUPS;
   static constexpr int THREADS = (EPI_WARP0 + 4) * 32;
-  static constexpr int ACC_BUFS = (2 * MT + (A_TMEM ? SA * 32 : 0) <= 512) ? 2 : 1;
+  static constexpr int A_SLOT_COLS = kStageK / 2;  // 64 columns of packed 16-bit pairs
+  static constexpr int ACC_BUFS = (2 * MT + (A_TMEM ? SA * A_SLOT_COLS : 0) <= 512) ? 2 : 1;
   static constexpr int A_COL0 = ACC_BUFS * MT;
-  static constexpr int USED_COLS = A_COL0 + (A_TMEM ? SA * 32 : 0);
+  static constexpr int USED_COLS = A_COL0 + (A_TMEM ? SA * A_SLOT_COLS : 0);
   static constexpr int TMEM_COLS = USED_COLS <= 32 ? 32 : USED_COLS <= 64 ? 64 : USED_COLS <= 128 ? 128 : USED_COLS <= 256 ? 256 : 512;
   static constexpr int X_STAGE = MT * 128;
-  static constexpr int A_STAGE = A_TMEM ? 0 : kTileN * 128;
+  static constexpr int A_HALF = kTileN * 128;              // one 64-K half of a shared-memory operand slot
+  static constexpr int A_STAGE = A_TMEM ? 0 : 2 * A_HALF;
   static constexpr int SMEM_X = 0;
   static constexpr int SMEM_A = SMEM_X + SX * X_STAGE;
   static constexpr int SMEM_W = SMEM_A + SA * A_STAGE;
@@ -90,6 +105,7 @@ struct GemmCfg {
   static_assert(USED_COLS <= 512, "tensor memory budget");
   static_assert(SMEM_ALLOC <= 232448, "shared memory budget");
   static_assert(2 * SW + 2 * SX + 2 * SA + 5 <= kNumBarrierSlots, "barrier slots");
+  static_assert(SX % 2 == 0, "two activation boxes per weight stage");
 };
 
 template <bool BF16>
@@ -117,6 +133,22 @@ HM_DEVICE void report_abort(int* status, int code, int a, int b) {
     __threadfence();
   }
 }
+
+// Ring position: index and phase parity, advanced without divisions.
+template <int DEPTH>
+struct Ring {
+  int idx = 0;
+  uint32_t phase = 0;
+  HM_DEVICE void advance() {
+    if (++idx == DEPTH) {
+      idx = 0;
+      phase ^= 1;
+    }
+  }
+  HM_DEVICE void advance_by(int n) {
+    for (int i = 0; i < n; ++i) advance();
+  }
+};
 
 template <int MT, bool BF16, bool HAS_ZP, bool A_TMEM>
 __global__ void __launch_bounds__(GemmCfg<MT, A_TMEM>::THREADS, 1)
@@ -198,33 +230,53 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
     // ------------------------------------------------ weight producer
     if (lane == 0) {
       const uint64_t pol = l2_policy_evict_first();
+      const uint32_t scale_bytes = p.groups_per_step * kScaleBytes;
+      const uint32_t zp_bytes = p.groups_per_step * kZpBytes;
+      const uint32_t tx_bytes = 2 * kCodeBytes + scale_bytes + (HAS_ZP ? zp_bytes : 0);
+      Ring<SW> ring;
       int it = 0;
       bool ok = true;
       while (ok && iter.next(seg)) {
-        const size_t tile_code0 = static_cast<size_t>(seg.n_tile) * p.sched.kb_per_tile;
-        const size_t tile_grp0 = static_cast<size_t>(seg.n_tile) * p.groups;
-        for (int kb = seg.kb0; kb < seg.kb1; ++kb, ++it) {
-          const int sw = it % SW;
-          const uint32_t ph = (it / SW) & 1;
-          if (!mbar_wait_bounded(w_empty(sw), ph ^ 1, abort_flag)) {
-            report_abort(p.status, HM_ABORT_W_EMPTY, it, sw);
+        const uint8_t* codes = p.w + (static_cast<size_t>(seg.n_tile) * p.sched.kb_per_tile + seg.kb0) * (2 * kCodeBytes);
+        // group cursor of step kb0
+        int g, cnt;
+        if (p.groups_per_step == 2) {
+          g = 2 * seg.kb0;
+          cnt = 0;
+        } else {
+          g = seg.kb0 / p.steps_per_group;
+          cnt = seg.kb0 - g * p.steps_per_group;
+        }
+        const uint8_t* scales = p.w_scale + (static_cast<size_t>(seg.n_tile) * p.groups + g) * kScaleBytes;
+        const uint8_t* zps = HAS_ZP ? p.w_zp + (static_cast<size_t>(seg.n_tile) * p.groups + g) * kZpBytes : nullptr;
+        for (int ks = seg.kb0; ks < seg.kb1; ++ks, ++it) {
+          if (!mbar_wait_bounded(w_empty(ring.idx), ring.phase ^ 1, abort_flag)) {
+            report_abort(p.status, HM_ABORT_W_EMPTY, it, ring.idx);
             ok = false;
             break;
           }
           trace(0, it, 0);
-          const uint32_t dst = w_smem + sw * kWStageBytes;
-          const int g = kb / p.kb_per_group;
+          const uint32_t dst = w_smem + ring.idx * kWStageBytes;
+          const uint32_t bar = w_full(ring.idx);
           if (p.dbg & HM_DBG_SKIP_W_LOAD) {
-            mbar_arrive(w_full(sw));
+            mbar_arrive(bar);
           } else {
-            mbar_arrive_expect_tx(w_full(sw), kCodeBytes + kScaleBytes + (HAS_ZP ? kZpBytes : 0));
-            bulk_g2s_hint(dst, p.w + (tile_code0 + kb) * kCodeBytes, kCodeBytes, w_full(sw), pol);
-            bulk_g2s(dst + kCodeBytes, p.w_scale + (tile_grp0 + g) * kScaleBytes, kScaleBytes, w_full(sw));
-            if constexpr (HAS_ZP) {
-              bulk_g2s(dst + kCodeBytes + kScaleBytes, p.w_zp + (tile_grp0 + g) * kZpBytes, kZpBytes, w_full(sw));
-            }
+            mbar_arrive_expect_tx(bar, tx_bytes);
+            bulk_g2s_hint(dst, codes, 2 * kCodeBytes, bar, pol);
+            bulk_g2s(dst + kWScaleOff, scales, scale_bytes, bar);
+            if constexpr (HAS_ZP) bulk_g2s(dst + kWZpOff, zps, zp_bytes, bar);
           }
           trace(0, it, 1);
+          codes += 2 * kCodeBytes;
+          if (p.groups_per_step == 2) {
+            scales += 2 * kScaleBytes;
+            if constexpr (HAS_ZP) zps += 2 * kZpBytes;
+          } else if (++cnt == p.steps_per_group) {
+            cnt = 0;
+            scales += kScaleBytes;
+            if constexpr (HAS_ZP) zps += kZpBytes;
+          }
+          ring.advance();
         }
       }
       if (!ok) {
@@ -238,25 +290,29 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
   } else if (warp == 1) {
     // ------------------------------------------------ activation producer
     if (lane == 0) {
-      int it = 0;
+      Ring<SX> ring;
+      int it = 0;  // counts 64-K boxes
       bool ok = true;
       while (ok && iter.next(seg)) {
-        for (int kb = seg.kb0; kb < seg.kb1; ++kb, ++it) {
-          const int s = it % SX;
-          const uint32_t ph = (it / SX) & 1;
-          if (!mbar_wait_bounded(x_empty(s), ph ^ 1, abort_flag)) {
-            report_abort(p.status, HM_ABORT_X_EMPTY, it, s);
+        const int row0 = seg.m_tile * MT;
+        int col = seg.kb0 * kStageK;
+        for (int kb = 2 * seg.kb0; kb < 2 * seg.kb1; ++kb, ++it) {
+          if (!mbar_wait_bounded(x_empty(ring.idx), ring.phase ^ 1, abort_flag)) {
+            report_abort(p.status, HM_ABORT_X_EMPTY, it, ring.idx);
             ok = false;
             break;
           }
           trace(1, it, 0);
+          const uint32_t bar = x_full(ring.idx);
           if (p.dbg & HM_DBG_SKIP_X_LOAD) {
-            mbar_arrive(x_full(s));
+            mbar_arrive(bar);
           } else {
-            mbar_arrive_expect_tx(x_full(s), Cfg::X_STAGE);
-            tma_load_2d(x_smem + s * Cfg::X_STAGE, &tmap_x, kb * kBlockK, seg.m_tile * MT, x_full(s));
+            mbar_arrive_expect_tx(bar, Cfg::X_STAGE);
+            tma_load_2d(x_smem + ring.idx * Cfg::X_STAGE, &tmap_x, col, row0, bar);
           }
           trace(1, it, 1);
+          col += kBlockK;
+          ring.advance();
         }
       }
       if (!ok) {
@@ -267,136 +323,180 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
       }
     }
   } else if (warp == 2) {
-    // ------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc(BF16 ? 1 : 0, BF16 ? 1 : 0, kTileN, MT);
-      int it = 0;
-      int sc = 0;
-      bool ok = true;
-      while (ok && iter.next(seg)) {
-        const int b = sc % ACC_BUFS;
-        const uint32_t acc_ph = (sc / ACC_BUFS) & 1;
-        if (!mbar_wait_bounded(acc_empty(b), acc_ph ^ 1, abort_flag)) {
-          report_abort(p.status, HM_ABORT_MMA_ACC, sc, b);
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + b * MT;
-        for (int kb = seg.kb0; kb < seg.kb1; ++kb, ++it) {
-          const int sx = it % SX;
-          const int sa = it % SA;
-          trace(2, it, 0);
-          const bool a_ok = mbar_wait_bounded(a_full(sa), (it / SA) & 1, abort_flag);
-          trace(2, it, 1);
-          if (!a_ok || !mbar_wait_bounded(x_full(sx), (it / SX) & 1, abort_flag)) {
-            report_abort(p.status, HM_ABORT_MMA_OPERANDS, it, sa);
+    // ------------------------------------------------ MMA issuer (whole warp, one lane issues)
+    constexpr uint32_t idesc = umma_idesc(BF16 ? 1 : 0, BF16 ? 1 : 0, kTileN, MT);
+    const uint64_t desc_hi = umma_desc_sw128(0) & 0xFFFFFFFF00000000ull;
+    const uint32_t desc_lo_const = static_cast<uint32_t>(umma_desc_sw128(0)) & 0xFFFFC000u;
+    Ring<SA> ra;
+    Ring<SX> rx;
+    int it = 0;  // counts 128-K steps
+    int sc = 0;
+    bool ok = true;
+    while (ok && iter.next(seg)) {
+      const int b = sc % ACC_BUFS;
+      const uint32_t acc_ph = (sc / ACC_BUFS) & 1;
+      if (!mbar_wait_bounded(acc_empty(b), acc_ph ^ 1, abort_flag)) {
+        if (lane == 0) report_abort(p.status, HM_ABORT_MMA_ACC, sc, b);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + b * MT;
+      for (int ks = seg.kb0; ks < seg.kb1; ++ks, ++it) {
+        Ring<SX> rx1 = rx;
+        rx1.advance();
+        if (lane == 0) trace(2, it, 0);
+        // Test the three barriers of this step back to back so that their round
+        // trips overlap; fall back to the bounded waits for whatever is not ready.
+        const bool r0 = mbar_try_wait(a_full(ra.idx), ra.phase);
+        const bool r1 = mbar_try_wait(x_full(rx.idx), rx.phase);
+        const bool r2 = mbar_try_wait(x_full(rx1.idx), rx1.phase);
+        if (!(r0 && r1 && r2)) {
+          if (!mbar_wait_bounded(a_full(ra.idx), ra.phase, abort_flag) ||
+              !mbar_wait_bounded(x_full(rx.idx), rx.phase, abort_flag) ||
+              !mbar_wait_bounded(x_full(rx1.idx), rx1.phase, abort_flag)) {
+            if (lane == 0) report_abort(p.status, HM_ABORT_MMA_OPERANDS, it, ra.idx);
             ok = false;
             break;
           }
-          trace(2, it, 2);
-          tc_fence_after();
-          const uint32_t xs = x_smem + sx * Cfg::X_STAGE;
-#pragma unroll
-          for (int k4 = 0; k4 < kBlockK / 16; ++k4) {
-            if (p.dbg & HM_DBG_SKIP_MMA) break;
-            const uint32_t accumulate = (kb != seg.kb0 || k4 != 0) ? 1u : 0u;
-            const uint64_t b_desc = umma_desc_sw128(xs, k4 * 32);
-            if constexpr (A_TMEM) {
-              mma_f16_ts(d_tmem, tmem_base + Cfg::A_COL0 + sa * 32 + k4 * 8, b_desc, idesc, accumulate);
-            } else {
-              mma_f16_ss(d_tmem, umma_desc_sw128(a_smem + sa * Cfg::A_STAGE, k4 * 32), b_desc, idesc, accumulate);
-            }
-          }
-          tc_commit(x_empty(sx));
-          tc_commit(a_empty(sa));
-          trace(2, it, 3);
         }
-        if (!ok) break;
-        tc_commit(acc_full(b));
-        ++sc;
+        if (lane == 0) trace(2, it, 1);
+        tc_fence_after();
+        {
+          // Operand addresses are computed by the whole warp (uniform values);
+          // only the tcgen05 instructions themselves are issued by one lane.
+          const bool issue = lane == 0 && !(p.dbg & HM_DBG_SKIP_MMA);
+          const uint32_t a_slot_tmem = tmem_base + Cfg::A_COL0 + ra.idx * Cfg::A_SLOT_COLS;
+          const uint32_t a_slot_smem = a_smem + ra.idx * Cfg::A_STAGE;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int sx = h == 0 ? rx.idx : rx1.idx;
+            const uint32_t b_lo = desc_lo_const | ((x_smem + sx * Cfg::X_STAGE) >> 4);
+            const uint32_t a_lo = desc_lo_const | ((a_slot_smem + h * Cfg::A_HALF) >> 4);
+#pragma unroll
+            for (int k4 = 0; k4 < 4; ++k4) {
+              const uint32_t accumulate = (ks != seg.kb0 || h != 0 || k4 != 0) ? 1u : 0u;
+              const uint64_t b_desc = desc_hi | static_cast<uint64_t>(b_lo + k4 * 2);
+              if (issue) {
+                if constexpr (A_TMEM) {
+                  mma_f16_ts(d_tmem, a_slot_tmem + h * 32 + k4 * 8, b_desc, idesc, accumulate);
+                } else {
+                  mma_f16_ss(d_tmem, desc_hi | static_cast<uint64_t>(a_lo + k4 * 2), b_desc, idesc, accumulate);
+                }
+              }
+            }
+            if (lane == 0) tc_commit(x_empty(sx));
+          }
+          if (lane == 0) tc_commit(a_empty(ra.idx));
+        }
+        if (lane == 0) trace(2, it, 3);
+        ra.advance();
+        rx.advance_by(2);
       }
-      if (!ok) {
-        // Abort path: wait for MMAs already issued before TMEM is released.
-        tc_commit(drain_bar);
-        mbar_wait_bounded(drain_bar, 0, abort_flag + 1);
-      }
+      if (!ok) break;
+      if (lane == 0) tc_commit(acc_full(b));
+      __syncwarp();
+      ++sc;
+    }
+    if (!ok && lane == 0) {
+      // Abort path: wait for MMAs already issued before TMEM is released.
+      tc_commit(drain_bar);
+      mbar_wait_bounded(drain_bar, 0, abort_flag + 1);
     }
   } else if (warp >= 4 && warp < Cfg::EPI_WARP0) {
     // ------------------------------------------------ dequant warps
-    const int group = (warp - 4) >> 2;  // groups take k-blocks round-robin
+    const int group = (warp - 4) >> 2;  // groups take stages round-robin
     const int q = warp & 3;             // TMEM lane quarter this warp may access
     const int row = q * 32 + lane;
+    const int half_group = p.groups_per_step == 2 ? 1 : 0;  // second 64-K half uses the stage's second group
+    // This group's first stage is `group`; afterwards it moves NGROUPS stages at a time.
+    Ring<SW> rw;
+    Ring<SA> ra;
+    rw.advance_by(group);
+    ra.advance_by(group);
     int it = 0;
     bool ok = true;
     while (ok && iter.next(seg)) {
-      for (int kb = seg.kb0; kb < seg.kb1; ++kb, ++it) {
+      for (int ks = seg.kb0; ks < seg.kb1; ++ks, ++it) {
         if ((it % NGROUPS) != group) continue;
-        const int sw = it % SW;
-        const int s = it % SA;
-        if (!mbar_wait_bounded(w_full(sw), (it / SW) & 1, abort_flag)) {
+        const int sw = rw.idx;
+        const int s = ra.idx;
+        if (!mbar_wait_bounded(w_full(sw), rw.phase, abort_flag)) {
           if (lane == 0) report_abort(p.status, HM_ABORT_DQ_W_FULL, it, sw);
           ok = false;
           break;
         }
         if (q == 0 && lane == 0) trace(3 + group, it, 0);
         const uint8_t* ws = smem_gen + Cfg::SMEM_W + sw * kWStageBytes;
-        const uint4 lo = *reinterpret_cast<const uint4*>(ws + row * 16);
-        const uint4 hi = *reinterpret_cast<const uint4*>(ws + 2048 + row * 16);
-        const uint32_t sc16 = *reinterpret_cast<const uint16_t*>(ws + kCodeBytes + row * 2);
-        const uint32_t scale2 = sc16 | (sc16 << 16);
-        uint32_t zp = 8;
-        if constexpr (HAS_ZP) {
-          zp = (ws[kCodeBytes + kScaleBytes + (row >> 1)] >> ((row & 1) * 4)) & 0xF;
-        }
-        const uint32_t zpm = zp_magic_pair<BF16>(zp);
-        uint32_t out[32];
-        if (p.dbg & HM_DBG_SKIP_MATH) {
+        uint4 codes[4];
+        codes[0] = *reinterpret_cast<const uint4*>(ws + row * 16);
+        codes[1] = *reinterpret_cast<const uint4*>(ws + 2048 + row * 16);
+        codes[2] = *reinterpret_cast<const uint4*>(ws + 4096 + row * 16);
+        codes[3] = *reinterpret_cast<const uint4*>(ws + 6144 + row * 16);
+        uint32_t scale2[2], zpm[2];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) out[i] = lo.x + i;
-        } else {
-        dequant_word_u4<BF16>(lo.x, zpm, scale2, out + 0);
-        dequant_word_u4<BF16>(lo.y, zpm, scale2, out + 4);
-        dequant_word_u4<BF16>(lo.z, zpm, scale2, out + 8);
-        dequant_word_u4<BF16>(lo.w, zpm, scale2, out + 12);
-        dequant_word_u4<BF16>(hi.x, zpm, scale2, out + 16);
-        dequant_word_u4<BF16>(hi.y, zpm, scale2, out + 20);
-        dequant_word_u4<BF16>(hi.z, zpm, scale2, out + 24);
-        dequant_word_u4<BF16>(hi.w, zpm, scale2, out + 28);
+        for (int h = 0; h < 2; ++h) {
+          const int gi = h * half_group;
+          const uint32_t sc16 = *reinterpret_cast<const uint16_t*>(ws + kWScaleOff + gi * kScaleBytes + row * 2);
+          scale2[h] = sc16 | (sc16 << 16);
+          uint32_t zp = 8;
+          if constexpr (HAS_ZP) zp = (ws[kWZpOff + gi * kZpBytes + (row >> 1)] >> ((row & 1) * 4)) & 0xF;
+          zpm[h] = zp_magic_pair<BF16>(zp);
         }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t out[32];
+          if (p.dbg & HM_DBG_SKIP_MATH) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) out[i] = codes[2 * h].x + i;
+          } else {
+            const uint32_t words[8] = {codes[2 * h].x,     codes[2 * h].y,     codes[2 * h].z,     codes[2 * h].w,
+                                       codes[2 * h + 1].x, codes[2 * h + 1].y, codes[2 * h + 1].z, codes[2 * h + 1].w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dequant_word_u4<BF16>(words[i], zpm[h], scale2[h], out + 4 * i);
+          }
+          if (h == 0) {
+            if (q == 0 && lane == 0) trace(3 + group, it, 1);
+            // Wait until the MMAs that read this operand slot last time are done.
+            if (!mbar_wait_bounded(a_empty(s), ra.phase ^ 1, abort_flag)) {
+              if (lane == 0) report_abort(p.status, HM_ABORT_DQ_SLOT, it, s);
+              ok = false;
+              break;
+            }
+            if (q == 0 && lane == 0) trace(3 + group, it, 2);
+            if constexpr (A_TMEM) tc_fence_after();
+          }
+          if constexpr (A_TMEM) {
+            if (!(p.dbg & HM_DBG_SKIP_TMEM_ST)) {
+              tmem_st_x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + Cfg::A_COL0 + s * Cfg::A_SLOT_COLS + h * 32, out);
+            } else if (out[5] == 0x12345u) {
+              p.status[7] = out[9];  // keep the math alive when the store is skipped
+            }
+          } else {
+            // 128-byte rows, 16-byte chunk c of row r stored at chunk (c ^ (r & 7)).
+            uint8_t* a_row = smem_gen + Cfg::SMEM_A + s * Cfg::A_STAGE + h * Cfg::A_HALF + (row >> 3) * 1024 + (row & 7) * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              *reinterpret_cast<uint4*>(a_row + ((c ^ (row & 7)) * 16)) =
+                  make_uint4(out[4 * c], out[4 * c + 1], out[4 * c + 2], out[4 * c + 3]);
+            }
+          }
+        }
+        if (!ok) break;
         // The packed stage has been consumed into registers: hand it back.
         __syncwarp();
         if (lane == 0) mbar_arrive(w_empty(sw));
-        if (q == 0 && lane == 0) trace(3 + group, it, 1);
-        // Wait until the MMAs that read this operand slot last time are done.
-        if (!mbar_wait_bounded(a_empty(s), ((it / SA) & 1) ^ 1, abort_flag)) {
-          if (lane == 0) report_abort(p.status, HM_ABORT_DQ_SLOT, it, s);
-          ok = false;
-          break;
-        }
-        if (q == 0 && lane == 0) trace(3 + group, it, 2);
         if constexpr (A_TMEM) {
-          tc_fence_after();
-          if (!(p.dbg & HM_DBG_SKIP_TMEM_ST)) {
-            tmem_st_x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + Cfg::A_COL0 + s * 32, out);
-            tc_wait_st();
-          } else if (out[5] == 0x12345u) {
-            p.status[7] = out[9];  // keep the math alive when the store is skipped
-          }
+          tc_wait_st();
           tc_fence_before();
         } else {
-          // 128-byte rows, 16-byte chunk c of row r stored at chunk (c ^ (r & 7)).
-          uint8_t* a_row = smem_gen + Cfg::SMEM_A + s * Cfg::A_STAGE + (row >> 3) * 1024 + (row & 7) * 128;
-#pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            *reinterpret_cast<uint4*>(a_row + ((c ^ (row & 7)) * 16)) =
-                make_uint4(out[4 * c], out[4 * c + 1], out[4 * c + 2], out[4 * c + 3]);
-          }
           fence_proxy_async_smem();
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(a_full(s));
         if (q == 0 && lane == 0) trace(3 + group, it, 3);
+        rw.advance_by(NGROUPS);
+        ra.advance_by(NGROUPS);
       }
     }
   } else if (warp >= Cfg::EPI_WARP0) {

@@ -74,12 +74,12 @@ class HummingLayerMeta(object):
             if self.c_dtype != self.a_dtype or self.bs_dtype != self.a_dtype:
                 no("c_dtype / bs_dtype different from a 16-bit a_dtype")
             g = self.weight_scale_group_size or self.shape_k
-            if g % 64:
-                no(f"weight_scale_group_size={g} (multiples of 64 only)")
+            if g != 64 and g % 128:
+                no(f"weight_scale_group_size={g} (64 or multiples of 128 only)")
         else:
             no(f"a_dtype={self.a_dtype}")
-        if self.shape_n % 128 or self.shape_k % 64:
-            no("shape_n not a multiple of 128 or shape_k not a multiple of 64")
+        if self.shape_n % 128 or self.shape_k % 128:
+            no("shape_n or shape_k not a multiple of 128")
         if self.has_dynamic_zp and self.b_dtype.is_signed:
             raise ValueError("dynamic zero point only supports uint weight dtypes")
 

@@ -83,10 +83,10 @@ typedef struct hm_plan {
   int32_t m_tile;         /* tokens per tile (UMMA N)                          */
   int32_t n_tiles;        /* shape_n / 128                                     */
   int32_t m_tiles;
-  int32_t kb_per_tile;    /* shape_k / 64                                      */
+  int32_t kb_per_tile;    /* shape_k / 128: K steps per tile                   */
   int32_t mode;           /* 0 = whole tiles round-robin, 1 = contiguous K-split */
   int32_t grid;           /* CTAs launched                                     */
-  int32_t units_per_cta;  /* mode 1: (tile, k-block) units per CTA             */
+  int32_t units_per_cta;  /* mode 1: (tile, K step) units per CTA              */
   int32_t reserved;
   int64_t total_units;
   int64_t workspace_bytes;

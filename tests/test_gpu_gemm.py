@@ -40,7 +40,7 @@ def test_m_sweep(cuda_device, dtype, zp, m):
     assert_close_16(out, ref, f"m={m}")
 
 
-@pytest.mark.parametrize("n,k,g", [(128, 64, 64), (128, 128, 128), (256, 4096, 128), (2048, 256, 64), (384, 1024, 0), (1536, 2048, 256)])
+@pytest.mark.parametrize("n,k,g", [(128, 128, 64), (128, 128, 128), (256, 4096, 128), (2048, 256, 64), (384, 1024, 0), (1536, 2048, 256)])
 def test_shapes_and_groups(cuda_device, n, k, g):
     case = synthetic.dense_w4a16_case(n, k, torch.bfloat16, True, group_size=g or k, seed=5)
     out, ref, _ = run_case(case, 48, cuda_device)

@@ -84,8 +84,11 @@ struct GemmCfg {
                                     : (MT <= 16 ? 24 : MT <= 32 ? 16 : MT <= 64 ? 12 : MT <= 128 ? 6 : 4);
   static constexpr int SA = A_TMEM ? 4 : 2;
   static constexpr int SW = MT <= 64 ? 8 : 4;
-  // Dequant warp groups (4 warps each) taking stages round-robin.
-  static constexpr int NGROUPS = 4;
+  // Dequant warp groups (4 warps each) taking stages round-robin.  A slot (and a
+  // weight stage) must always be refilled by the group that filled it before:
+  // phase-parity waits cannot tell a barrier that is two phases behind from one
+  // that is current, so no group may run ahead of another on the same barrier.
+  static constexpr int NGROUPS = A_TMEM ? 4 : 2;
   static constexpr int EPI_WARP0 = 4 + 4 * NGROUPS;
   static constexpr int THREADS = (EPI_WARP0 + 4) * 32;
   static constexpr int A_SLOT_COLS = kStageK / 2;  // 64 columns of packed 16-bit pairs
@@ -106,6 +109,7 @@ struct GemmCfg {
   static_assert(SMEM_ALLOC <= 232448, "shared memory budget");
   static_assert(2 * SW + 2 * SX + 2 * SA + 5 <= kNumBarrierSlots, "barrier slots");
   static_assert(SX % 2 == 0, "two activation boxes per weight stage");
+  static_assert(SA % NGROUPS == 0 && SW % NGROUPS == 0, "each ring slot belongs to one dequant group");
 };
 
 template <bool BF16>
@@ -386,6 +390,7 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
               }
             }
             if (lane == 0) tc_commit(x_empty(sx));
+            if (lane == 0 && h == 0) trace(2, it, 2);
           }
           if (lane == 0) tc_commit(a_empty(ra.idx));
         }

@@ -349,6 +349,7 @@ int hm_gemm(const hm_gemm_desc* desc, int64_t m, const void* a, int64_t lda, con
   if (desc->has_bias && bias == nullptr) return fail(HM_ERR_INVALID, "bias is NULL but the descriptor has a bias");
   if (lda < desc->shape_k || ldc < desc->shape_n) return fail(HM_ERR_INVALID, "lda/ldc smaller than the row length");
   if ((reinterpret_cast<uintptr_t>(a) & 15) || ((lda * 2) & 15)) return fail(HM_ERR_INVALID, "activations must be 16-byte aligned with a 16-byte row pitch");
+  if ((reinterpret_cast<uintptr_t>(c) & 15) || (ldc & 7)) return fail(HM_ERR_INVALID, "output must be 16-byte aligned with a 16-byte row pitch");
   if ((reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(w_scale) & 15) || (reinterpret_cast<uintptr_t>(w_zp) & 15))
     return fail(HM_ERR_INVALID, "prepared weight buffers must be 16-byte aligned");
   if (workspace == nullptr || workspace_bytes < static_cast<size_t>(pl.workspace_bytes))

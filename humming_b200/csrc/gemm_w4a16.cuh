@@ -92,8 +92,12 @@ struct GemmCfg {
   static constexpr int EPI_WARP0 = 4 + 4 * NGROUPS;
   static constexpr int THREADS = (EPI_WARP0 + 4) * 32;
   static constexpr int A_SLOT_COLS = kStageK / 2;  // 64 columns of packed 16-bit pairs
-  static constexpr int ACC_BUFS = (2 * MT + (A_TMEM ? SA * A_SLOT_COLS : 0) <= 512) ? 2 : 1;
-  static constexpr int A_COL0 = ACC_BUFS * MT;
+  // Interleaved accumulators: consecutive K=16 MMAs go to different TMEM
+  // accumulators (summed in the epilogue) so that a small token tile is not
+  // bound by the latency of back-to-back MMAs on one accumulator.
+  static constexpr int NACC = MT <= 32 ? 4 : MT <= 64 ? 2 : 1;
+  static constexpr int ACC_BUFS = (2 * NACC * MT + (A_TMEM ? SA * A_SLOT_COLS : 0) <= 512) ? 2 : 1;
+  static constexpr int A_COL0 = ACC_BUFS * NACC * MT;
   static constexpr int USED_COLS = A_COL0 + (A_TMEM ? SA * A_SLOT_COLS : 0);
   static constexpr int TMEM_COLS = USED_COLS <= 32 ? 32 : USED_COLS <= 64 ? 64 : USED_COLS <= 128 ? 128 : USED_COLS <= 256 ? 256 : 512;
   static constexpr int X_STAGE = MT * 128;
@@ -102,7 +106,8 @@ struct GemmCfg {
   static constexpr int SMEM_X = 0;
   static constexpr int SMEM_A = SMEM_X + SX * X_STAGE;
   static constexpr int SMEM_W = SMEM_A + SA * A_STAGE;
-  static constexpr int SMEM_BAR = SMEM_W + SW * kWStageBytes;
+  static constexpr int SMEM_STAGE = SMEM_W + SW * kWStageBytes;  // epilogue transpose staging, 2 KB per warp
+  static constexpr int SMEM_BAR = SMEM_STAGE + 4 * 2048;
   static constexpr int SMEM_TOTAL = SMEM_BAR + kNumBarrierSlots * 8 + 64;
   static constexpr int SMEM_ALLOC = SMEM_TOTAL + 1024;  // slack for manual 1024-byte alignment
   static_assert(USED_COLS <= 512, "tensor memory budget");
@@ -345,7 +350,7 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
         break;
       }
       tc_fence_after();
-      const uint32_t d_tmem = tmem_base + b * MT;
+      const uint32_t d_tmem = tmem_base + b * (Cfg::NACC * MT);
       for (int ks = seg.kb0; ks < seg.kb1; ++ks, ++it) {
         Ring<SX> rx1 = rx;
         rx1.advance();
@@ -379,13 +384,16 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
             const uint32_t a_lo = desc_lo_const | ((a_slot_smem + h * Cfg::A_HALF) >> 4);
 #pragma unroll
             for (int k4 = 0; k4 < 4; ++k4) {
-              const uint32_t accumulate = (ks != seg.kb0 || h != 0 || k4 != 0) ? 1u : 0u;
+              constexpr int kNacc = Cfg::NACC;
+              const int j = h * 4 + k4;  // K=16 slice within the step
+              const uint32_t accumulate = (ks != seg.kb0 || j >= kNacc) ? 1u : 0u;
+              const uint32_t d_acc = d_tmem + (j % kNacc) * MT;
               const uint64_t b_desc = desc_hi | static_cast<uint64_t>(b_lo + k4 * 2);
               if (issue) {
                 if constexpr (A_TMEM) {
-                  mma_f16_ts(d_tmem, a_slot_tmem + h * 32 + k4 * 8, b_desc, idesc, accumulate);
+                  mma_f16_ts(d_acc, a_slot_tmem + h * 32 + k4 * 8, b_desc, idesc, accumulate);
                 } else {
-                  mma_f16_ss(d_tmem, desc_hi | static_cast<uint64_t>(a_lo + k4 * 2), b_desc, idesc, accumulate);
+                  mma_f16_ss(d_acc, desc_hi | static_cast<uint64_t>(a_lo + k4 * 2), b_desc, idesc, accumulate);
                 }
               }
             }
@@ -523,24 +531,54 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
       const int m_valid = (p.M - m0) < MT ? (p.M - m0) : MT;
       const float bias = (p.bias != nullptr) ? load_bias<BF16>(p.bias, n) : 0.f;
       float* slot = p.partials + static_cast<size_t>(seg.slot) * (MT * kTileN);
-      const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + b * MT;
+      const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + b * (Cfg::NACC * MT);
+      constexpr int CH = MT >= 32 ? 32 : 16;  // token columns per chunk
+      uint8_t* stage = smem_gen + Cfg::SMEM_STAGE + q * 2048;  // this warp's [CH tokens][32 rows] 16-bit tile
 #pragma unroll 1
-      for (int c0 = 0; c0 < MT; c0 += 16) {
+      for (int c0 = 0; c0 < MT; c0 += CH) {
         if (c0 >= m_valid) break;  // warp-uniform
-        uint32_t v[16];
-        tmem_ld_x16(t_acc + c0, v);
-        tc_wait_ld();
-        if (!seg.partial) {
+        float v[CH];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
+        for (int a = 0; a < Cfg::NACC; ++a) {
+          uint32_t r[CH];
+          if constexpr (CH == 32) {
+            tmem_ld_x32(t_acc + a * MT + c0, r);
+          } else {
+            tmem_ld_x16(t_acc + a * MT + c0, r);
+          }
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < CH; ++j) v[j] = (a == 0) ? __uint_as_float(r[j]) : v[j] + __uint_as_float(r[j]);
+        }
+        if (!seg.partial) {
+          // Transpose through shared memory so that global stores are 16 bytes per
+          // lane: lane = weight row writes one 16-bit value per token into the
+          // staging tile; then 4 lanes cover the 64 bytes of one token's 32 rows.
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < CH; ++j) {
+            const float o = v[j] + bias;
+            if constexpr (BF16) {
+              reinterpret_cast<__nv_bfloat16*>(stage)[j * 32 + lane] = __float2bfloat16_rn(o);
+            } else {
+              reinterpret_cast<__half*>(stage)[j * 32 + lane] = __float2half_rn(o);
+            }
+          }
+          __syncwarp();
+          const int n_base = seg.n_tile * kTileN + q * 32;
+#pragma unroll
+          for (int i = 0; i < CH / 8; ++i) {
+            const int j = i * 8 + (lane >> 2);
             if (c0 + j < m_valid) {
-              store_out<BF16>(p.c, static_cast<size_t>(m0 + c0 + j) * p.ldc + n, __uint_as_float(v[j]) + bias);
+              const uint4 val = *reinterpret_cast<const uint4*>(stage + j * 64 + (lane & 3) * 16);
+              uint8_t* dst = static_cast<uint8_t*>(p.c) + (static_cast<size_t>(m0 + c0 + j) * p.ldc + n_base) * 2 + (lane & 3) * 16;
+              *reinterpret_cast<uint4*>(dst) = val;
             }
           }
         } else {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            if (c0 + j < m_valid) slot[(c0 + j) * kTileN + row] = __uint_as_float(v[j]);
+          for (int j = 0; j < CH; ++j) {
+            if (c0 + j < m_valid) slot[(c0 + j) * kTileN + row] = v[j];
           }
         }
       }

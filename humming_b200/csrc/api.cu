@@ -81,8 +81,9 @@ int validate_desc(const hm_gemm_desc* d) {
   } else {
     return fail(HM_ERR_UNSUPPORTED, "a_dtype code %d not built", d->a_dtype);
   }
-  if (d->m_tile != 0 && d->m_tile != 16 && d->m_tile != 32 && d->m_tile != 64 && d->m_tile != 128 && d->m_tile != 256)
-    return fail(HM_ERR_INVALID, "m_tile must be 0, 16, 32, 64, 128 or 256");
+  if (d->m_tile != 0 && d->m_tile != 16 && d->m_tile != 32 && d->m_tile != 64 && d->m_tile != 128 && d->m_tile != 192 &&
+      d->m_tile != 256)
+    return fail(HM_ERR_INVALID, "m_tile must be 0, 16, 32, 64, 128, 192 or 256");
   if (d->num_experts != 0) return fail(HM_ERR_UNSUPPORTED, "MoE layers go through hm_moe_gemm");
   return HM_OK;
 }
@@ -97,7 +98,21 @@ int make_plan(const hm_gemm_desc* d, int64_t m, hm_plan* plan) {
     if (rc != HM_OK) return rc;
   }
   int mt = d->m_tile;
-  if (mt == 0) mt = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : m <= 128 ? 128 : 256;
+  if (mt == 0) {
+    if (m <= 256) {
+      mt = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : m <= 128 ? 128 : 256;
+    } else {
+      // 192-token tiles have two accumulators (epilogue overlapped with the next
+      // tile's main loop); 256-token tiles amortise the dequant over more tokens
+      // but drain their single accumulator in the open (~12 % of a tile).  Pick by
+      // padded work.
+      const double w192 = static_cast<double>((m + 191) / 192) * 192.0;
+      const double w256 = static_cast<double>((m + 255) / 256) * 256.0 * 1.12;
+      mt = w192 <= w256 ? 192 : 256;
+    }
+  }
+  if ((d->flags & HM_FLAG_A_OPERAND_SMEM) && mt > 128)
+    return fail(HM_ERR_UNSUPPORTED, "the shared-memory operand variant is built for token tiles up to 128");
   memset(plan, 0, sizeof(*plan));
   plan->m_tile = mt;
   plan->n_tiles = d->shape_n / hm::kTileN;
@@ -168,8 +183,11 @@ int dispatch_gemm(bool bf16, bool zp, bool a_tmem, const hm::GemmParams& p, cons
     if (bf16) return zp ? launch_gemm<MT, true, true, true>(p, tmap, grid, stream) : launch_gemm<MT, true, false, true>(p, tmap, grid, stream);
     return zp ? launch_gemm<MT, false, true, true>(p, tmap, grid, stream) : launch_gemm<MT, false, false, true>(p, tmap, grid, stream);
   }
-  if (bf16) return zp ? launch_gemm<MT, true, true, false>(p, tmap, grid, stream) : launch_gemm<MT, true, false, false>(p, tmap, grid, stream);
-  return zp ? launch_gemm<MT, false, true, false>(p, tmap, grid, stream) : launch_gemm<MT, false, false, false>(p, tmap, grid, stream);
+  if constexpr (MT <= 128) {
+    if (bf16) return zp ? launch_gemm<MT, true, true, false>(p, tmap, grid, stream) : launch_gemm<MT, true, false, false>(p, tmap, grid, stream);
+    return zp ? launch_gemm<MT, false, true, false>(p, tmap, grid, stream) : launch_gemm<MT, false, false, false>(p, tmap, grid, stream);
+  }
+  return fail(HM_ERR_UNSUPPORTED, "no shared-memory operand kernel for m_tile=%d", MT);
 }
 
 inline unsigned blocks_for(int64_t n, int threads) { return static_cast<unsigned>((n + threads - 1) / threads); }
@@ -400,6 +418,7 @@ int hm_gemm(const hm_gemm_desc* desc, int64_t m, const void* a, int64_t lda, con
     case 32: return dispatch_gemm<32>(bf16, desc->has_zp != 0, a_tmem, p, tmap, pl.grid, s);
     case 64: return dispatch_gemm<64>(bf16, desc->has_zp != 0, a_tmem, p, tmap, pl.grid, s);
     case 128: return dispatch_gemm<128>(bf16, desc->has_zp != 0, a_tmem, p, tmap, pl.grid, s);
+    case 192: return dispatch_gemm<192>(bf16, desc->has_zp != 0, a_tmem, p, tmap, pl.grid, s);
     case 256: return dispatch_gemm<256>(bf16, desc->has_zp != 0, a_tmem, p, tmap, pl.grid, s);
   }
   return fail(HM_ERR_INVALID, "no kernel for m_tile=%d", pl.m_tile);

@@ -5,26 +5,29 @@
 // *B* operand (m_tile tokens = UMMA N, 16..256), so the same kernel covers
 // decode (M = 1..64, HBM-bound) and prefill (M in the thousands, tensor-bound).
 //
-//   warp 0        weight producer: 1-D bulk copies of packed codes + group
-//                 scales (+ zero points) for 128 K-elements per stage into a
-//                 shared-memory ring
-//   warp 1        activation producer: 2-D TMA boxes (64 K x m_tile rows,
-//                 128-byte swizzle) into a second, deeper ring
-//   warp 2        MMA issuer: tcgen05.mma kind::f16, fp32 accumulators in TMEM.
-//                 The whole warp runs the loop (uniform control flow, so
-//                 descriptors live in uniform registers); one lane issues.
-//   warp 3        TMEM allocation / release
-//   warps 4..19   dequant: thread = weight row; 64 bytes of codes -> 128 values
-//                 of the activation type, written straight into tensor memory
-//                 (tcgen05.st) where the MMA reads them as its A operand --
-//                 the expanded weights never touch shared memory.  Four groups
-//                 of four warps take stages round-robin.
-//   warps 20..23  epilogue: tcgen05.ld -> (+bias) -> cast -> global, or fp32
-//                 partials + last-arriver reduction when K is split
+//   warp 0        weight producer: one 1-D bulk copy of packed codes (8 KB =
+//                 128 rows x 128 K-elements) per stage into a shared-memory ring
+//   warp 1        activation producer: two 2-D TMA boxes (64 K x m_tile rows,
+//                 128-byte swizzle) per stage into a second, deeper ring
+//   warp 2        MMA issuer: tcgen05.mma kind::f16, fp32 accumulators in TMEM
+//   warp 3        TMEM allocation / release; producer of the group scales and
+//                 zero points that belong to each weight stage
+//   next 4*G      dequant warps (G groups of four; G = 4, or 2 for the 192-token
+//                 tile): thread = weight row; 64 bytes of codes -> 128 values of
+//                 the activation type, written straight into tensor memory
+//                 (tcgen05.st) where the MMA reads them as its A operand -- the
+//                 expanded weights never touch shared memory.  Groups take
+//                 stages round-robin and own their ring slots.
+//   last 4        epilogue: tcgen05.ld -> (+bias) -> cast -> shared-memory
+//                 transpose -> 16-byte global stores, or fp32 partials +
+//                 last-arriver reduction when K is split
 //
-// The single-thread roles are latency-bound on their own instruction streams
-// (an mbarrier test costs ~100 cycles round trip), so a stage carries 128
-// K-elements and the loops avoid everything but increments.
+// Measured on B200: one tcgen05.mma (M=128, K=16) cannot issue faster than
+// every ~45-52 cycles whatever N is, an mbarrier test is a ~100-cycle round
+// trip and every TMA/bulk/commit instruction costs its issuing thread several
+// tens of cycles.  Hence 128 K-elements per stage, single-thread loops that do
+// nothing but increments, the next stage's barriers probed before the current
+// stage's MMAs are issued, and the per-stage copies spread over three warps.
 //
 // Replaces the reference's humming<> kernel
 // (humming/include/humming/kernel/humming_ws.cuh:25-176) and its pipelines
@@ -76,31 +79,33 @@ struct GemmParams {
 
 template <int MT, bool A_TMEM>
 struct GemmCfg {
-  // Ring depths: SX activation boxes (64 K each, shared memory; deep for small
-  // token tiles where a box is tiny and L2 latency must be covered), SA operand
-  // slots for the dequantized weights (128 K each: 64 TMEM columns, or 32 KB of
-  // shared memory in the cross-check variant), SW packed-weight stages (128 K).
-  static constexpr int SX = !A_TMEM ? (MT <= 32 ? 8 : MT <= 128 ? 4 : 2)
-                                    : (MT <= 16 ? 24 : MT <= 32 ? 16 : MT <= 64 ? 12 : MT <= 128 ? 6 : 4);
-  static constexpr int SA = A_TMEM ? 4 : 2;
+  static_assert(MT == 16 || MT == 32 || MT == 64 || MT == 128 || MT == 192 || MT == 256, "token tile");
+  static_assert(A_TMEM || MT <= 128, "the shared-memory operand variant is built for tiles up to 128 tokens");
+  // Ring depths, all in 128-K stages: SX activation stages (two 64-K boxes each,
+  // shared memory; deep for small token tiles where a stage is tiny and L2
+  // latency must be covered), SA operand slots for the dequantized weights
+  // (64 TMEM columns, or 32 KB of shared memory in the cross-check variant),
+  // SW packed-weight stages.
+  static constexpr int SX = !A_TMEM ? (MT <= 32 ? 4 : MT <= 64 ? 3 : 2)
+                                    : (MT <= 16 ? 12 : MT <= 32 ? 8 : MT <= 64 ? 6 : MT <= 192 ? 3 : 2);
+  static constexpr int SA = (!A_TMEM || MT == 192) ? 2 : 4;
   static constexpr int SW = MT <= 64 ? 8 : 4;
   // Dequant warp groups (4 warps each) taking stages round-robin.  A slot (and a
   // weight stage) must always be refilled by the group that filled it before:
   // phase-parity waits cannot tell a barrier that is two phases behind from one
   // that is current, so no group may run ahead of another on the same barrier.
-  static constexpr int NGROUPS = A_TMEM ? 4 : 2;
+  static constexpr int NGROUPS = SA;
   static constexpr int EPI_WARP0 = 4 + 4 * NGROUPS;
   static constexpr int THREADS = (EPI_WARP0 + 4) * 32;
   static constexpr int A_SLOT_COLS = kStageK / 2;  // 64 columns of packed 16-bit pairs
-  // Interleaved accumulators: consecutive K=16 MMAs go to different TMEM
-  // accumulators (summed in the epilogue) so that a small token tile is not
-  // bound by the latency of back-to-back MMAs on one accumulator.
-  static constexpr int NACC = MT <= 32 ? 4 : MT <= 64 ? 2 : 1;
-  static constexpr int ACC_BUFS = (2 * NACC * MT + (A_TMEM ? SA * A_SLOT_COLS : 0) <= 512) ? 2 : 1;
-  static constexpr int A_COL0 = ACC_BUFS * NACC * MT;
+  // Two accumulators let the epilogue of one tile overlap the main loop of the
+  // next; the 256-token tile has no TMEM left for a second one.
+  static constexpr int ACC_BUFS = (2 * MT + (A_TMEM ? SA * A_SLOT_COLS : 0) <= 512) ? 2 : 1;
+  static constexpr int A_COL0 = ACC_BUFS * MT;
   static constexpr int USED_COLS = A_COL0 + (A_TMEM ? SA * A_SLOT_COLS : 0);
   static constexpr int TMEM_COLS = USED_COLS <= 32 ? 32 : USED_COLS <= 64 ? 64 : USED_COLS <= 128 ? 128 : USED_COLS <= 256 ? 256 : 512;
-  static constexpr int X_STAGE = MT * 128;
+  static constexpr int X_BOX = MT * 128;                   // one 64-K box
+  static constexpr int X_STAGE = 2 * X_BOX;
   static constexpr int A_HALF = kTileN * 128;              // one 64-K half of a shared-memory operand slot
   static constexpr int A_STAGE = A_TMEM ? 0 : 2 * A_HALF;
   static constexpr int SMEM_X = 0;
@@ -113,7 +118,6 @@ struct GemmCfg {
   static_assert(USED_COLS <= 512, "tensor memory budget");
   static_assert(SMEM_ALLOC <= 232448, "shared memory budget");
   static_assert(2 * SW + 2 * SX + 2 * SA + 5 <= kNumBarrierSlots, "barrier slots");
-  static_assert(SX % 2 == 0, "two activation boxes per weight stage");
   static_assert(SA % NGROUPS == 0 && SW % NGROUPS == 0, "each ring slot belongs to one dequant group");
 };
 
@@ -196,7 +200,7 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < SW; ++i) {
-      mbar_init(w_full(i), 1);
+      mbar_init(w_full(i), 2);  // code producer + scale/zero-point producer
       mbar_init(w_empty(i), 4);
     }
     for (int i = 0; i < SX; ++i) {
@@ -236,17 +240,51 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
   };
 
   if (warp == 0) {
-    // ------------------------------------------------ weight producer
+    // ------------------------------------------------ weight producer (packed codes)
     if (lane == 0) {
       const uint64_t pol = l2_policy_evict_first();
-      const uint32_t scale_bytes = p.groups_per_step * kScaleBytes;
-      const uint32_t zp_bytes = p.groups_per_step * kZpBytes;
-      const uint32_t tx_bytes = 2 * kCodeBytes + scale_bytes + (HAS_ZP ? zp_bytes : 0);
       Ring<SW> ring;
       int it = 0;
       bool ok = true;
       while (ok && iter.next(seg)) {
         const uint8_t* codes = p.w + (static_cast<size_t>(seg.n_tile) * p.sched.kb_per_tile + seg.kb0) * (2 * kCodeBytes);
+        for (int ks = seg.kb0; ks < seg.kb1; ++ks, ++it) {
+          if (!mbar_wait_bounded(w_empty(ring.idx), ring.phase ^ 1, abort_flag)) {
+            report_abort(p.status, HM_ABORT_W_EMPTY, it, ring.idx);
+            ok = false;
+            break;
+          }
+          trace(0, it, 0);
+          const uint32_t bar = w_full(ring.idx);
+          if (p.dbg & HM_DBG_SKIP_W_LOAD) {
+            mbar_arrive(bar);
+          } else {
+            mbar_arrive_expect_tx(bar, 2 * kCodeBytes);
+            bulk_g2s_hint(w_smem + ring.idx * kWStageBytes, codes, 2 * kCodeBytes, bar, pol);
+          }
+          trace(0, it, 1);
+          codes += 2 * kCodeBytes;
+          ring.advance();
+        }
+      }
+      if (!ok) {
+        // Abort path: let copies already issued land before the CTA exits.
+        for (int j = 0; j < SW && j < it; ++j) {
+          const int last_it = it - 1 - j;
+          mbar_wait_bounded(w_full(last_it % SW), (last_it / SW) & 1, abort_flag + 1);
+        }
+      }
+    }
+  } else if (warp == 3) {
+    // ------------------------------------------------ scale / zero-point producer
+    if (lane == 0) {
+      const uint32_t scale_bytes = p.groups_per_step * kScaleBytes;
+      const uint32_t zp_bytes = p.groups_per_step * kZpBytes;
+      const uint32_t tx_bytes = scale_bytes + (HAS_ZP ? zp_bytes : 0);
+      Ring<SW> ring;
+      int it = 0;
+      bool ok = true;
+      while (ok && iter.next(seg)) {
         // group cursor of step kb0
         int g, cnt;
         if (p.groups_per_step == 2) {
@@ -264,19 +302,15 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
             ok = false;
             break;
           }
-          trace(0, it, 0);
           const uint32_t dst = w_smem + ring.idx * kWStageBytes;
           const uint32_t bar = w_full(ring.idx);
           if (p.dbg & HM_DBG_SKIP_W_LOAD) {
             mbar_arrive(bar);
           } else {
             mbar_arrive_expect_tx(bar, tx_bytes);
-            bulk_g2s_hint(dst, codes, 2 * kCodeBytes, bar, pol);
             bulk_g2s(dst + kWScaleOff, scales, scale_bytes, bar);
             if constexpr (HAS_ZP) bulk_g2s(dst + kWZpOff, zps, zp_bytes, bar);
           }
-          trace(0, it, 1);
-          codes += 2 * kCodeBytes;
           if (p.groups_per_step == 2) {
             scales += 2 * kScaleBytes;
             if constexpr (HAS_ZP) zps += 2 * kZpBytes;
@@ -289,7 +323,6 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
         }
       }
       if (!ok) {
-        // Abort path: let copies already issued land before the CTA exits.
         for (int j = 0; j < SW && j < it; ++j) {
           const int last_it = it - 1 - j;
           mbar_wait_bounded(w_full(last_it % SW), (last_it / SW) & 1, abort_flag + 1);
@@ -300,12 +333,12 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
     // ------------------------------------------------ activation producer
     if (lane == 0) {
       Ring<SX> ring;
-      int it = 0;  // counts 64-K boxes
+      int it = 0;
       bool ok = true;
       while (ok && iter.next(seg)) {
         const int row0 = seg.m_tile * MT;
         int col = seg.kb0 * kStageK;
-        for (int kb = 2 * seg.kb0; kb < 2 * seg.kb1; ++kb, ++it) {
+        for (int ks = seg.kb0; ks < seg.kb1; ++ks, ++it) {
           if (!mbar_wait_bounded(x_empty(ring.idx), ring.phase ^ 1, abort_flag)) {
             report_abort(p.status, HM_ABORT_X_EMPTY, it, ring.idx);
             ok = false;
@@ -316,11 +349,13 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
           if (p.dbg & HM_DBG_SKIP_X_LOAD) {
             mbar_arrive(bar);
           } else {
+            const uint32_t dst = x_smem + ring.idx * Cfg::X_STAGE;
             mbar_arrive_expect_tx(bar, Cfg::X_STAGE);
-            tma_load_2d(x_smem + ring.idx * Cfg::X_STAGE, &tmap_x, col, row0, bar);
+            tma_load_2d(dst, &tmap_x, col, row0, bar);
+            tma_load_2d(dst + Cfg::X_BOX, &tmap_x, col + kBlockK, row0, bar);
           }
           trace(1, it, 1);
-          col += kBlockK;
+          col += kStageK;
           ring.advance();
         }
       }
@@ -332,13 +367,15 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
       }
     }
   } else if (warp == 2) {
-    // ------------------------------------------------ MMA issuer (whole warp, one lane issues)
+    // ------------------------------------------------ MMA issuer
+    // The whole warp follows the loop and the barrier waits; lane 0 issues.
     constexpr uint32_t idesc = umma_idesc(BF16 ? 1 : 0, BF16 ? 1 : 0, kTileN, MT);
     const uint64_t desc_hi = umma_desc_sw128(0) & 0xFFFFFFFF00000000ull;
     const uint32_t desc_lo_const = static_cast<uint32_t>(umma_desc_sw128(0)) & 0xFFFFC000u;
     Ring<SA> ra;
     Ring<SX> rx;
-    int it = 0;  // counts 128-K steps
+    bool ready = false;  // operands of the coming step already seen complete by the look-ahead probe
+    int it = 0;
     int sc = 0;
     bool ok = true;
     while (ok && iter.next(seg)) {
@@ -349,21 +386,12 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
         ok = false;
         break;
       }
-      tc_fence_after();
-      const uint32_t d_tmem = tmem_base + b * (Cfg::NACC * MT);
+      const uint32_t d_tmem = tmem_base + b * MT;
       for (int ks = seg.kb0; ks < seg.kb1; ++ks, ++it) {
-        Ring<SX> rx1 = rx;
-        rx1.advance();
         if (lane == 0) trace(2, it, 0);
-        // Test the three barriers of this step back to back so that their round
-        // trips overlap; fall back to the bounded waits for whatever is not ready.
-        const bool r0 = mbar_try_wait(a_full(ra.idx), ra.phase);
-        const bool r1 = mbar_try_wait(x_full(rx.idx), rx.phase);
-        const bool r2 = mbar_try_wait(x_full(rx1.idx), rx1.phase);
-        if (!(r0 && r1 && r2)) {
+        if (!ready) {
           if (!mbar_wait_bounded(a_full(ra.idx), ra.phase, abort_flag) ||
-              !mbar_wait_bounded(x_full(rx.idx), rx.phase, abort_flag) ||
-              !mbar_wait_bounded(x_full(rx1.idx), rx1.phase, abort_flag)) {
+              !mbar_wait_bounded(x_full(rx.idx), rx.phase, abort_flag)) {
             if (lane == 0) report_abort(p.status, HM_ABORT_MMA_OPERANDS, it, ra.idx);
             ok = false;
             break;
@@ -371,40 +399,38 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
         }
         if (lane == 0) trace(2, it, 1);
         tc_fence_after();
-        {
-          // Operand addresses are computed by the whole warp (uniform values);
-          // only the tcgen05 instructions themselves are issued by one lane.
-          const bool issue = lane == 0 && !(p.dbg & HM_DBG_SKIP_MMA);
-          const uint32_t a_slot_tmem = tmem_base + Cfg::A_COL0 + ra.idx * Cfg::A_SLOT_COLS;
-          const uint32_t a_slot_smem = a_smem + ra.idx * Cfg::A_STAGE;
+        // Probe the next step's barriers now: the round trip overlaps with the
+        // issue of this step's MMAs, and a hit skips the blocking wait next time.
+        Ring<SA> na = ra;
+        Ring<SX> nx = rx;
+        na.advance();
+        nx.advance();
+        const bool probe = mbar_test_wait(a_full(na.idx), na.phase) && mbar_test_wait(x_full(nx.idx), nx.phase);
+        if (lane == 0) {
+          if (!(p.dbg & HM_DBG_SKIP_MMA)) {
+            const uint32_t a_slot_tmem = tmem_base + Cfg::A_COL0 + ra.idx * Cfg::A_SLOT_COLS;
+            const uint32_t b_lo0 = desc_lo_const | ((x_smem + rx.idx * Cfg::X_STAGE) >> 4);
+            const uint32_t a_lo0 = desc_lo_const | ((a_smem + ra.idx * Cfg::A_STAGE) >> 4);
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const int sx = h == 0 ? rx.idx : rx1.idx;
-            const uint32_t b_lo = desc_lo_const | ((x_smem + sx * Cfg::X_STAGE) >> 4);
-            const uint32_t a_lo = desc_lo_const | ((a_slot_smem + h * Cfg::A_HALF) >> 4);
-#pragma unroll
-            for (int k4 = 0; k4 < 4; ++k4) {
-              constexpr int kNacc = Cfg::NACC;
-              const int j = h * 4 + k4;  // K=16 slice within the step
-              const uint32_t accumulate = (ks != seg.kb0 || j >= kNacc) ? 1u : 0u;
-              const uint32_t d_acc = d_tmem + (j % kNacc) * MT;
-              const uint64_t b_desc = desc_hi | static_cast<uint64_t>(b_lo + k4 * 2);
-              if (issue) {
-                if constexpr (A_TMEM) {
-                  mma_f16_ts(d_acc, a_slot_tmem + h * 32 + k4 * 8, b_desc, idesc, accumulate);
-                } else {
-                  mma_f16_ss(d_acc, desc_hi | static_cast<uint64_t>(a_lo + k4 * 2), b_desc, idesc, accumulate);
-                }
+            for (int j = 0; j < 8; ++j) {  // eight K=16 slices of the 128-K stage
+              const int h = j >> 2, k4 = j & 3;
+              const uint32_t accumulate = (ks != seg.kb0 || j != 0) ? 1u : 0u;
+              const uint64_t b_desc = desc_hi | static_cast<uint64_t>(b_lo0 + h * (Cfg::X_BOX >> 4) + k4 * 2);
+              if constexpr (A_TMEM) {
+                mma_f16_ts(d_tmem, a_slot_tmem + j * 8, b_desc, idesc, accumulate);
+              } else {
+                mma_f16_ss(d_tmem, desc_hi | static_cast<uint64_t>(a_lo0 + h * (Cfg::A_HALF >> 4) + k4 * 2), b_desc, idesc, accumulate);
               }
             }
-            if (lane == 0) tc_commit(x_empty(sx));
-            if (lane == 0 && h == 0) trace(2, it, 2);
           }
-          if (lane == 0) tc_commit(a_empty(ra.idx));
+          tc_commit(x_empty(rx.idx));
+          tc_commit(a_empty(ra.idx));
+          trace(2, it, 3);
         }
-        if (lane == 0) trace(2, it, 3);
-        ra.advance();
-        rx.advance_by(2);
+        __syncwarp();
+        ready = __all_sync(0xffffffffu, probe);
+        ra = na;
+        rx = nx;
       }
       if (!ok) break;
       if (lane == 0) tc_commit(acc_full(b));
@@ -531,24 +557,23 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
       const int m_valid = (p.M - m0) < MT ? (p.M - m0) : MT;
       const float bias = (p.bias != nullptr) ? load_bias<BF16>(p.bias, n) : 0.f;
       float* slot = p.partials + static_cast<size_t>(seg.slot) * (MT * kTileN);
-      const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + b * (Cfg::NACC * MT);
+      const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + b * MT;
       constexpr int CH = MT >= 32 ? 32 : 16;  // token columns per chunk
       uint8_t* stage = smem_gen + Cfg::SMEM_STAGE + q * 2048;  // this warp's [CH tokens][32 rows] 16-bit tile
 #pragma unroll 1
       for (int c0 = 0; c0 < MT; c0 += CH) {
         if (c0 >= m_valid) break;  // warp-uniform
         float v[CH];
-#pragma unroll
-        for (int a = 0; a < Cfg::NACC; ++a) {
+        {
           uint32_t r[CH];
           if constexpr (CH == 32) {
-            tmem_ld_x32(t_acc + a * MT + c0, r);
+            tmem_ld_x32(t_acc + c0, r);
           } else {
-            tmem_ld_x16(t_acc + a * MT + c0, r);
+            tmem_ld_x16(t_acc + c0, r);
           }
           tc_wait_ld();
 #pragma unroll
-          for (int j = 0; j < CH; ++j) v[j] = (a == 0) ? __uint_as_float(r[j]) : v[j] + __uint_as_float(r[j]);
+          for (int j = 0; j < CH; ++j) v[j] = __uint_as_float(r[j]);
         }
         if (!seg.partial) {
           // Transpose through shared memory so that global stores are 16 bytes per

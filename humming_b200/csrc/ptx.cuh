@@ -61,6 +61,19 @@ HM_DEVICE bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking probe of a barrier phase (never suspends the thread).
+HM_DEVICE bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Wall-clock limit of one wait.  Legitimate waits in these kernels are at most
 // a few hundred microseconds (one tile's main loop).
 constexpr uint64_t kWaitLimitNs = 2000000000ull;

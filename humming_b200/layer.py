@@ -23,7 +23,7 @@ from humming_b200 import runtime
 from humming_b200.utils.weight import prepare_humming_tensor_for_glu, quantize_weight
 
 _FLOAT_DTYPES = (torch.float16, torch.bfloat16, torch.float32)
-_M_TILES = (16, 32, 64, 128, 256)
+_M_TILES = (16, 32, 64, 128, 192, 256)
 
 
 @dataclasses.dataclass
@@ -321,7 +321,7 @@ class HummingMethod(torch.nn.Module):
                           sublayer_name: str = "", **kwargs):
         """Force a token tile for ``min_shape_m <= M <= max_shape_m``
         (``humming/layer.py:453-499``).  ``block_shape[0]`` is rounded up to a
-        tile this library has (16, 32, 64, 128, 256); N/K block sizes and
+        tile this library has (16, 32, 64, 128, 192, 256); N/K block sizes and
         ``warp_shape`` have no counterpart and are ignored."""
         m_tile = next((t for t in _M_TILES if t >= block_shape[0]), 256)
         layer.humming_block_size_configs[sublayer_name] += [min_shape_m, max_shape_m, m_tile]

@@ -65,13 +65,14 @@ typedef struct hm_gemm_desc {
   int32_t num_experts;  /* 0 = dense layer                                          */
   int32_t top_k;        /* MoE only                                                 */
   int32_t is_moe_down;  /* MoE only: read row = id, multiply by topk weight         */
-  int32_t m_tile;       /* token tile override (16..256); 0 = choose from M         */
+  int32_t m_tile;       /* token tile override (16,32,64,128,192,256); 0 = from M   */
   int32_t num_sms;      /* CTAs to launch at most; 0 = every SM of the device       */
   int32_t flags;        /* HM_FLAG_*                                                */
 } hm_gemm_desc;
 
 /* Stage the dequantized weight tile in shared memory instead of tensor memory
- * (slower; kept as a cross-check of the tensor-memory operand path). */
+ * (slower; kept as a cross-check of the tensor-memory operand path; token
+ * tiles up to 128 only). */
 #define HM_FLAG_A_OPERAND_SMEM 1
 /* Never split a tile's K range over several CTAs (batch-invariant results, the
  * counterpart of use_stream_k=False, docs/CONFIG.md "Scheduler Config"). */

@@ -99,17 +99,10 @@ int make_plan(const hm_gemm_desc* d, int64_t m, hm_plan* plan) {
   }
   int mt = d->m_tile;
   if (mt == 0) {
-    if (m <= 256) {
-      mt = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : m <= 128 ? 128 : 256;
-    } else {
-      // 192-token tiles have two accumulators (epilogue overlapped with the next
-      // tile's main loop); 256-token tiles amortise the dequant over more tokens
-      // but drain their single accumulator in the open (~12 % of a tile).  Pick by
-      // padded work.
-      const double w192 = static_cast<double>((m + 191) / 192) * 192.0;
-      const double w256 = static_cast<double>((m + 255) / 256) * 256.0 * 1.12;
-      mt = w192 <= w256 ? 192 : 256;
-    }
+    // The 192-token tile (two accumulators, epilogue overlapped) measured slower
+    // than the 256-token tile (one accumulator) on B200, so it is used only on
+    // request.
+    mt = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : m <= 128 ? 128 : 256;
   }
   if ((d->flags & HM_FLAG_A_OPERAND_SMEM) && mt > 128)
     return fail(HM_ERR_UNSUPPORTED, "the shared-memory operand variant is built for token tiles up to 128");

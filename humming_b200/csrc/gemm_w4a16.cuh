@@ -81,14 +81,14 @@ template <int MT, bool A_TMEM>
 struct GemmCfg {
   static_assert(MT == 16 || MT == 32 || MT == 64 || MT == 128 || MT == 192 || MT == 256, "token tile");
   static_assert(A_TMEM || MT <= 128, "the shared-memory operand variant is built for tiles up to 128 tokens");
-  // Ring depths, all in 128-K stages: SX activation stages (two 64-K boxes each,
-  // shared memory; deep for small token tiles where a stage is tiny and L2
-  // latency must be covered), SA operand slots for the dequantized weights
-  // (64 TMEM columns, or 32 KB of shared memory in the cross-check variant),
-  // SW packed-weight stages.
-  static constexpr int SX = !A_TMEM ? (MT <= 32 ? 4 : MT <= 64 ? 3 : 2)
-                                    : (MT <= 16 ? 12 : MT <= 32 ? 8 : MT <= 64 ? 6 : MT <= 192 ? 3 : 2);
+  // Ring depths, all in 128-K stages: SA operand slots for the dequantized
+  // weights (64 TMEM columns, or 32 KB of shared memory in the cross-check
+  // variant), SX activation stages (two 64-K boxes each, shared memory), SW
+  // packed-weight stages.
   static constexpr int SA = (!A_TMEM || MT == 192) ? 2 : 4;
+  // An activation stage is released by the same tcgen05.commit as the operand
+  // slot of its step (one commit per step), so its ring cannot be deeper.
+  static constexpr int SX = MT <= 128 ? SA : 2;
   static constexpr int SW = MT <= 64 ? 8 : 4;
   // Dequant warp groups (4 warps each) taking stages round-robin.  A slot (and a
   // weight stage) must always be refilled by the group that filled it before:
@@ -117,8 +117,9 @@ struct GemmCfg {
   static constexpr int SMEM_ALLOC = SMEM_TOTAL + 1024;  // slack for manual 1024-byte alignment
   static_assert(USED_COLS <= 512, "tensor memory budget");
   static_assert(SMEM_ALLOC <= 232448, "shared memory budget");
-  static_assert(2 * SW + 2 * SX + 2 * SA + 5 <= kNumBarrierSlots, "barrier slots");
+  static_assert(2 * SW + SX + 2 * SA + 5 <= kNumBarrierSlots, "barrier slots");
   static_assert(SA % NGROUPS == 0 && SW % NGROUPS == 0, "each ring slot belongs to one dequant group");
+  static_assert(SX <= SA, "activation stages are released through the operand-slot barriers");
 };
 
 template <bool BF16>
@@ -185,10 +186,11 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
   auto w_full = [&](int i) { return bar0 + 8u * i; };
   auto w_empty = [&](int i) { return bar0 + 8u * (SW + i); };
   auto x_full = [&](int i) { return bar0 + 8u * (2 * SW + i); };
-  auto x_empty = [&](int i) { return bar0 + 8u * (2 * SW + SX + i); };
-  auto a_full = [&](int i) { return bar0 + 8u * (2 * SW + 2 * SX + i); };
-  auto a_empty = [&](int i) { return bar0 + 8u * (2 * SW + 2 * SX + SA + i); };
-  constexpr int kBarAcc = 2 * SW + 2 * SX + 2 * SA;
+  auto a_full = [&](int i) { return bar0 + 8u * (2 * SW + SX + i); };
+  // a_empty(slot): the MMAs of the step that used operand slot `slot` (and the
+  // activation stage of that step) have completed.
+  auto a_empty = [&](int i) { return bar0 + 8u * (2 * SW + SX + SA + i); };
+  constexpr int kBarAcc = 2 * SW + SX + 2 * SA;
   auto acc_full = [&](int i) { return bar0 + 8u * (kBarAcc + i); };
   auto acc_empty = [&](int i) { return bar0 + 8u * (kBarAcc + 2 + i); };
   const uint32_t drain_bar = bar0 + 8u * (kBarAcc + 4);
@@ -203,10 +205,7 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
       mbar_init(w_full(i), 2);  // code producer + scale/zero-point producer
       mbar_init(w_empty(i), 4);
     }
-    for (int i = 0; i < SX; ++i) {
-      mbar_init(x_full(i), 1);
-      mbar_init(x_empty(i), 1);
-    }
+    for (int i = 0; i < SX; ++i) mbar_init(x_full(i), 1);
     for (int i = 0; i < SA; ++i) {
       mbar_init(a_full(i), 4);
       mbar_init(a_empty(i), 1);
@@ -333,16 +332,20 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
     // ------------------------------------------------ activation producer
     if (lane == 0) {
       Ring<SX> ring;
+      Ring<SA> done;  // operand-slot barrier of step (it - SX), whose completion frees stage ring.idx
       int it = 0;
       bool ok = true;
       while (ok && iter.next(seg)) {
         const int row0 = seg.m_tile * MT;
         int col = seg.kb0 * kStageK;
         for (int ks = seg.kb0; ks < seg.kb1; ++ks, ++it) {
-          if (!mbar_wait_bounded(x_empty(ring.idx), ring.phase ^ 1, abort_flag)) {
-            report_abort(p.status, HM_ABORT_X_EMPTY, it, ring.idx);
-            ok = false;
-            break;
+          if (it >= SX) {
+            if (!mbar_wait_bounded(a_empty(done.idx), done.phase, abort_flag)) {
+              report_abort(p.status, HM_ABORT_X_EMPTY, it, ring.idx);
+              ok = false;
+              break;
+            }
+            done.advance();
           }
           trace(1, it, 0);
           const uint32_t bar = x_full(ring.idx);
@@ -399,13 +402,6 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
         }
         if (lane == 0) trace(2, it, 1);
         tc_fence_after();
-        // Probe the next step's barriers now: the round trip overlaps with the
-        // issue of this step's MMAs, and a hit skips the blocking wait next time.
-        Ring<SA> na = ra;
-        Ring<SX> nx = rx;
-        na.advance();
-        nx.advance();
-        const bool probe = mbar_test_wait(a_full(na.idx), na.phase) && mbar_test_wait(x_full(nx.idx), nx.phase);
         if (lane == 0) {
           if (!(p.dbg & HM_DBG_SKIP_MMA)) {
             const uint32_t a_slot_tmem = tmem_base + Cfg::A_COL0 + ra.idx * Cfg::A_SLOT_COLS;
@@ -423,14 +419,18 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
               }
             }
           }
-          tc_commit(x_empty(rx.idx));
+          // One commit per step: frees the operand slot and the activation stage.
           tc_commit(a_empty(ra.idx));
           trace(2, it, 3);
         }
         __syncwarp();
-        ready = __all_sync(0xffffffffu, probe);
-        ra = na;
-        rx = nx;
+        ra.advance();
+        rx.advance();
+        // Probe the next step's barriers while this step's MMAs execute; a hit
+        // skips the blocking wait (a ~100-cycle round trip each) next time.
+        const bool probe_a = mbar_test_wait(a_full(ra.idx), ra.phase);
+        const bool probe_x = mbar_test_wait(x_full(rx.idx), rx.phase);
+        ready = __all_sync(0xffffffffu, probe_a & probe_x);
       }
       if (!ok) break;
       if (lane == 0) tc_commit(acc_full(b));

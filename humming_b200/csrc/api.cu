@@ -9,6 +9,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include "gemm_w4a16.cuh"
 #include "prep.cuh"
@@ -415,6 +416,61 @@ int hm_gemm(const hm_gemm_desc* desc, int64_t m, const void* a, int64_t lda, con
     case 256: return dispatch_gemm<256>(bf16, desc->has_zp != 0, a_tmem, p, tmap, pl.grid, s);
   }
   return fail(HM_ERR_INVALID, "no kernel for m_tile=%d", pl.m_tile);
+}
+
+// ---- hm_gemm_static_scratch ------------------------------------------------------
+// Scratch for callers that cannot allocate.  It is part of the library's device
+// image: each GPU that loads the library carries HM_STATIC_SCRATCH_BYTES of it
+// until the process exits.  In host code `g_static_scratch` is only a handle for
+// cudaGetSymbolAddress; the kernel must be given the looked-up device address.
+static __device__ __align__(256) unsigned char g_static_scratch[HM_STATIC_SCRATCH_BYTES];
+
+namespace {
+std::mutex g_static_scratch_mutex;
+unsigned char* g_static_scratch_addr[64] = {nullptr};  // per device, filled on first use
+
+// Device address of the static scratch on the current device.  The first call
+// per device asks the runtime for it (and must therefore not happen while a
+// stream is being captured); later calls read the cached value.
+int static_scratch_address(unsigned char** out) {
+  int dev = 0;
+  HM_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(HM_ERR_CUDA, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_addr[dev] == nullptr) {
+    unsigned char* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr)
+      return fail(HM_ERR_CUDA, "cudaGetSymbolAddress(static scratch) failed on device %d: %s", dev, cudaGetErrorString(e));
+    g_static_scratch_addr[dev] = ptr;
+  }
+  *out = g_static_scratch_addr[dev];
+  return HM_OK;
+}
+}  // namespace
+
+int hm_gemm_static_scratch(const hm_gemm_desc* desc, int64_t m, const void* a, int64_t lda, const float* a_scale,
+                           const void* w, const void* w_scale, const void* w_zp, const void* bias, void* c,
+                           int64_t ldc, void* stream) {
+  hm_plan pl;
+  int rc = make_plan(desc, m, &pl);
+  if (rc != HM_OK) return rc;
+  if (m == 0) return HM_OK;
+  if (static_cast<uint64_t>(pl.workspace_bytes) > HM_STATIC_SCRATCH_BYTES)
+    return fail(HM_ERR_WORKSPACE,
+                "this shape needs %lld bytes of scratch but the built-in array holds %u; call hm_gemm with a caller-owned workspace",
+                static_cast<long long>(pl.workspace_bytes), static_cast<unsigned>(HM_STATIC_SCRATCH_BYTES));
+  unsigned char* scratch = nullptr;
+  rc = static_scratch_address(&scratch);
+  if (rc != HM_OK) return rc;
+  // The array still holds the previous call's partial sums, possibly laid out for
+  // another shape: the status words and tile counters of *this* plan must read
+  // zero when the kernel starts.  (The partial-sum slots need no clearing, every
+  // slot is written before it is read.)
+  const int64_t tiles = static_cast<int64_t>(pl.n_tiles) * pl.m_tiles;
+  const size_t zero_bytes = 256 + (pl.mode == 1 ? static_cast<size_t>(((tiles * 16 + 255) / 256) * 256) : 0);
+  HM_CUDA_OK(cudaMemsetAsync(scratch, 0, zero_bytes, static_cast<cudaStream_t>(stream)));
+  return hm_gemm(desc, m, a, lda, a_scale, w, w_scale, w_zp, bias, c, ldc, scratch, HM_STATIC_SCRATCH_BYTES, stream);
 }
 
 int hm_check_status(void* workspace, size_t workspace_bytes, void* stream) {

@@ -16,6 +16,8 @@ HM_ERR_WORKSPACE = -3
 HM_ERR_CUDA = -4
 HM_ERR_DEVICE = -5
 
+HM_STATIC_SCRATCH_BYTES = 8 << 20
+
 HM_FLAG_A_OPERAND_SMEM = 1
 HM_FLAG_NO_SPLIT_K = 2
 
@@ -53,6 +55,7 @@ SIGNATURES = {
     "hm_gemm_plan": (_I, [_DESC, _L, ctypes.POINTER(Plan)]),
     "hm_gemm_workspace_bytes": (ctypes.c_size_t, [_DESC, _L]),
     "hm_gemm": (_I, [_DESC, _L, _P, _L, _P, _P, _P, _P, _P, _P, _L, _P, ctypes.c_size_t, _P]),
+    "hm_gemm_static_scratch": (_I, [_DESC, _L, _P, _L, _P, _P, _P, _P, _P, _P, _L, _P]),
     "hm_check_status": (_I, [_P, ctypes.c_size_t, _P]),
     "hm_last_error": (ctypes.c_char_p, []),
     "hm_version": (_I, []),

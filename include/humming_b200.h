@@ -159,6 +159,36 @@ HM_API int hm_gemm(const hm_gemm_desc* desc, int64_t m, const void* a, int64_t l
                    const void* w, const void* w_scale, const void* w_zp, const void* bias, void* c, int64_t ldc,
                    void* workspace, size_t workspace_bytes, void* stream);
 
+/* Same computation as hm_gemm for callers that cannot provide a workspace.
+ * No counterpart in the reference implementation.
+ *
+ * Who needs it: code that runs where device allocation is off limits -- a
+ * decode step being recorded into a CUDA graph, a plugin that is handed fixed
+ * input/output buffers by a host engine and has no allocator of its own, a
+ * real-time loop that may not call into the driver's allocator.  Such callers
+ * have nowhere to get the split-K scratch that hm_gemm asks for.
+ *
+ * The scratch lives in a fixed array of HM_STATIC_SCRATCH_BYTES inside the
+ * library's device image (every GPU that loads the library holds that much
+ * memory until the process exits).  The call allocates nothing: no cudaMalloc,
+ * no cudaFree, no allocating library routine.  Shapes whose launch plan needs
+ * more scratch than the array holds (roughly: more than 32 rows on large
+ * layers) are refused with HM_ERR_WORKSPACE and a message that states both
+ * sizes; use hm_gemm with your own workspace for those.
+ *
+ * The first call on each device looks up the array's device address (with that
+ * device current) and remembers it; make that first call outside any stream
+ * capture.  All calls share the one array and it keeps whatever the previous
+ * call left there; the counters that must start at zero are cleared on
+ * `stream` before every launch.  Two calls whose kernels can overlap on the
+ * GPU (different streams, or concurrent threads) race on the array: serialise
+ * them on one stream.  Device-side aborts of this variant are not reported;
+ * hm_check_status works only on caller-owned workspaces. */
+#define HM_STATIC_SCRATCH_BYTES (8u << 20)
+HM_API int hm_gemm_static_scratch(const hm_gemm_desc* desc, int64_t m, const void* a, int64_t lda,
+                                  const float* a_scale, const void* w, const void* w_scale, const void* w_zp,
+                                  const void* bias, void* c, int64_t ldc, void* stream);
+
 /* Reads the workspace's status words back (synchronises `stream`); returns
  * HM_ERR_DEVICE and resets the workspace if the last kernels using it aborted. */
 HM_API int hm_check_status(void* workspace, size_t workspace_bytes, void* stream);

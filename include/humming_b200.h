@@ -163,10 +163,10 @@ HM_API int hm_gemm(const hm_gemm_desc* desc, int64_t m, const void* a, int64_t l
  * No counterpart in the reference implementation.
  *
  * Who needs it: code that runs where device allocation is off limits -- a
- * decode step being recorded into a CUDA graph, a plugin that is handed fixed
- * input/output buffers by a host engine and has no allocator of its own, a
- * real-time loop that may not call into the driver's allocator.  Such callers
- * have nowhere to get the split-K scratch that hm_gemm asks for.
+ * serving loop whose memory pool is frozen after warm-up, a plugin that is
+ * handed fixed input/output buffers by a host engine and has no allocator of
+ * its own, a real-time loop that may not call into the driver's allocator.
+ * Such callers have nowhere to get the split-K scratch that hm_gemm asks for.
  *
  * The scratch lives in a fixed array of HM_STATIC_SCRATCH_BYTES inside the
  * library's device image (every GPU that loads the library holds that much

@@ -1,7 +1,7 @@
 """hm_gemm_static_scratch: the GEMM entry point for callers that cannot allocate.
 
 Some callers of this library have no way to obtain device memory at call time:
-a decode step that is being recorded into a CUDA graph, or a plugin that a host
+a serving loop whose memory pool is frozen after warm-up, or a plugin that a host
 engine hands fixed buffers and no allocator.  For them the library carries an
 8 MiB scratch array inside its own device image.  This test drives that entry
 point straight through the C ABI and checks it against the regular hm_gemm

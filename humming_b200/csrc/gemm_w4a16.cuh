@@ -238,6 +238,7 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
     if (tracing && idx < kTraceEvents) p.trace[(role * kTraceEvents + idx) * 4 + j] = clock64();
   };
 
+  if (threadIdx.x == 0) trace(7, 0, 0);
   if (warp == 0) {
     // ------------------------------------------------ weight producer (packed codes)
     if (lane == 0) {
@@ -370,77 +371,72 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
       }
     }
   } else if (warp == 2) {
-    // ------------------------------------------------ MMA issuer
-    // The whole warp follows the loop and the barrier waits; lane 0 issues.
-    constexpr uint32_t idesc = umma_idesc(BF16 ? 1 : 0, BF16 ? 1 : 0, kTileN, MT);
-    const uint64_t desc_hi = umma_desc_sw128(0) & 0xFFFFFFFF00000000ull;
-    const uint32_t desc_lo_const = static_cast<uint32_t>(umma_desc_sw128(0)) & 0xFFFFC000u;
-    Ring<SA> ra;
-    Ring<SX> rx;
-    bool ready = false;  // operands of the coming step already seen complete by the look-ahead probe
-    int it = 0;
-    int sc = 0;
-    bool ok = true;
-    while (ok && iter.next(seg)) {
-      const int b = sc % ACC_BUFS;
-      const uint32_t acc_ph = (sc / ACC_BUFS) & 1;
-      if (!mbar_wait_bounded(acc_empty(b), acc_ph ^ 1, abort_flag)) {
-        if (lane == 0) report_abort(p.status, HM_ABORT_MMA_ACC, sc, b);
-        ok = false;
-        break;
-      }
-      const uint32_t d_tmem = tmem_base + b * MT;
-      for (int ks = seg.kb0; ks < seg.kb1; ++ks, ++it) {
-        if (lane == 0) trace(2, it, 0);
-        if (!ready) {
-          if (!mbar_wait_bounded(a_full(ra.idx), ra.phase, abort_flag) ||
-              !mbar_wait_bounded(x_full(rx.idx), rx.phase, abort_flag)) {
-            if (lane == 0) report_abort(p.status, HM_ABORT_MMA_OPERANDS, it, ra.idx);
-            ok = false;
-            break;
-          }
+    // ------------------------------------------------ MMA issuer (one thread)
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(BF16 ? 1 : 0, BF16 ? 1 : 0, kTileN, MT);
+      const uint64_t desc_hi = umma_desc_sw128(0) & 0xFFFFFFFF00000000ull;
+      const uint32_t desc_lo_const = static_cast<uint32_t>(umma_desc_sw128(0)) & 0xFFFFC000u;
+      Ring<SA> ra;
+      Ring<SX> rx;
+      bool ready = false;  // operands of the coming step already seen complete by the look-ahead probe
+      int it = 0;
+      int sc = 0;
+      bool ok = true;
+      while (ok && iter.next(seg)) {
+        const int b = sc % ACC_BUFS;
+        const uint32_t acc_ph = (sc / ACC_BUFS) & 1;
+        if (!mbar_wait_bounded(acc_empty(b), acc_ph ^ 1, abort_flag)) {
+          report_abort(p.status, HM_ABORT_MMA_ACC, sc, b);
+          ok = false;
+          break;
         }
-        if (lane == 0) trace(2, it, 1);
-        tc_fence_after();
-        if (lane == 0) {
-          if (!(p.dbg & HM_DBG_SKIP_MMA)) {
-            const uint32_t a_slot_tmem = tmem_base + Cfg::A_COL0 + ra.idx * Cfg::A_SLOT_COLS;
-            const uint32_t b_lo0 = desc_lo_const | ((x_smem + rx.idx * Cfg::X_STAGE) >> 4);
-            const uint32_t a_lo0 = desc_lo_const | ((a_smem + ra.idx * Cfg::A_STAGE) >> 4);
+        const uint32_t d_tmem = tmem_base + b * MT;
+        for (int ks = seg.kb0; ks < seg.kb1; ++ks, ++it) {
+          trace(2, it, 0);
+          if (!ready) {
+            if (!mbar_wait_bounded(a_full(ra.idx), ra.phase, abort_flag) ||
+                !mbar_wait_bounded(x_full(rx.idx), rx.phase, abort_flag)) {
+              report_abort(p.status, HM_ABORT_MMA_OPERANDS, it, ra.idx);
+              ok = false;
+              break;
+            }
+          }
+          trace(2, it, 1);
+          tc_fence_after();
+          const uint32_t slot = ra.idx;
+          const uint32_t b_lo0 = desc_lo_const | ((x_smem + rx.idx * Cfg::X_STAGE) >> 4);
+          ra.advance();
+          rx.advance();
+          const uint32_t acc0 = ks != seg.kb0 ? 1u : 0u;
+          if constexpr (A_TMEM) {
+            // MMAs + commit + look-ahead probe of the next step's barriers in one block.
+            ready = mma_step_f16_ts(d_tmem, tmem_base + Cfg::A_COL0 + slot * Cfg::A_SLOT_COLS, desc_hi | b_lo0,
+                                    Cfg::X_BOX >> 4, idesc, acc0, a_empty(slot), a_full(ra.idx), ra.phase,
+                                    x_full(rx.idx), rx.phase, (p.dbg & HM_DBG_SKIP_MMA) != 0);
+          } else {
+            const uint32_t a_lo0 = desc_lo_const | ((a_smem + slot * Cfg::A_STAGE) >> 4);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {  // eight K=16 slices of the 128-K stage
               const int h = j >> 2, k4 = j & 3;
-              const uint32_t accumulate = (ks != seg.kb0 || j != 0) ? 1u : 0u;
               const uint64_t b_desc = desc_hi | static_cast<uint64_t>(b_lo0 + h * (Cfg::X_BOX >> 4) + k4 * 2);
-              if constexpr (A_TMEM) {
-                mma_f16_ts(d_tmem, a_slot_tmem + j * 8, b_desc, idesc, accumulate);
-              } else {
-                mma_f16_ss(d_tmem, desc_hi | static_cast<uint64_t>(a_lo0 + h * (Cfg::A_HALF >> 4) + k4 * 2), b_desc, idesc, accumulate);
-              }
+              mma_f16_ss(d_tmem, desc_hi | static_cast<uint64_t>(a_lo0 + h * (Cfg::A_HALF >> 4) + k4 * 2), b_desc, idesc,
+                         (j != 0) ? 1u : acc0);
             }
+            // One commit per step: frees the operand slot and the activation stage.
+            tc_commit(a_empty(slot));
+            ready = false;
           }
-          // One commit per step: frees the operand slot and the activation stage.
-          tc_commit(a_empty(ra.idx));
           trace(2, it, 3);
         }
-        __syncwarp();
-        ra.advance();
-        rx.advance();
-        // Probe the next step's barriers while this step's MMAs execute; a hit
-        // skips the blocking wait (a ~100-cycle round trip each) next time.
-        const bool probe_a = mbar_test_wait(a_full(ra.idx), ra.phase);
-        const bool probe_x = mbar_test_wait(x_full(rx.idx), rx.phase);
-        ready = __all_sync(0xffffffffu, probe_a & probe_x);
+        if (!ok) break;
+        tc_commit(acc_full(b));
+        ++sc;
       }
-      if (!ok) break;
-      if (lane == 0) tc_commit(acc_full(b));
-      __syncwarp();
-      ++sc;
-    }
-    if (!ok && lane == 0) {
-      // Abort path: wait for MMAs already issued before TMEM is released.
-      tc_commit(drain_bar);
-      mbar_wait_bounded(drain_bar, 0, abort_flag + 1);
+      if (!ok) {
+        // Abort path: wait for MMAs already issued before TMEM is released.
+        tc_commit(drain_bar);
+        mbar_wait_bounded(drain_bar, 0, abort_flag + 1);
+      }
     }
   } else if (warp >= 4 && warp < Cfg::EPI_WARP0) {
     // ------------------------------------------------ dequant warps
@@ -552,6 +548,7 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
         break;
       }
       tc_fence_after();
+      if (q == 0 && lane == 0) trace(7, sc + 1, 0);
       const int n = seg.n_tile * kTileN + row;
       const int m0 = seg.m_tile * MT;
       const int m_valid = (p.M - m0) < MT ? (p.M - m0) : MT;
@@ -611,6 +608,7 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty(b));
+      if (q == 0 && lane == 0) trace(7, sc + 1, 1);
       ++sc;
 
       if (seg.partial) {
@@ -658,6 +656,7 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
   // Every role ends here, also after an abort (all waits are bounded).
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) trace(7, 0, 3);
   if (warp == 3) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);

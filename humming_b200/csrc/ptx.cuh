@@ -179,6 +179,65 @@ HM_DEVICE void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uin
       "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// One 128-K pipeline step of the A-from-TMEM GEMM as a single instruction
+// block: probe the next step's two barriers (non-blocking), issue the eight
+// K=16 MMAs, commit, and only then read the probe results -- so the ~100-cycle
+// barrier round trips overlap with the MMA issue instead of preceding it.
+//   a_tmem: first column of the 64-column operand slot (8 columns per MMA)
+//   b_desc: descriptor of the first 64-K activation box; box_step: descriptor
+//           increment to the second box ((box bytes) >> 4)
+//   acc0:   0 = the first MMA overwrites the accumulator
+// Returns true if both probed barriers had completed their phase.
+HM_DEVICE bool mma_step_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t box_step, uint32_t idesc,
+                               uint32_t acc0, uint32_t commit_bar, uint32_t next_bar_a, uint32_t next_par_a,
+                               uint32_t next_bar_x, uint32_t next_par_x, bool skip_mma) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred pacc, pone, pna, pnx, pskip;\n\t"
+      ".reg .b32 a1, a2, a3, a4, a5, a6, a7;\n\t"
+      ".reg .b64 b1, b2, b3, b4, b5, b6, b7, bs;\n\t"
+      "setp.ne.b32 pacc, %6, 0;\n\t"
+      "setp.eq.b32 pone, 0, 0;\n\t"
+      "setp.ne.b32 pskip, %12, 0;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 pna, [%8], %9;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 pnx, [%10], %11;\n\t"
+      "add.u32 a1, %2, 8;\n\t"
+      "add.u32 a2, %2, 16;\n\t"
+      "add.u32 a3, %2, 24;\n\t"
+      "add.u32 a4, %2, 32;\n\t"
+      "add.u32 a5, %2, 40;\n\t"
+      "add.u32 a6, %2, 48;\n\t"
+      "add.u32 a7, %2, 56;\n\t"
+      "cvt.u64.u32 bs, %4;\n\t"
+      "add.u64 b1, %3, 2;\n\t"
+      "add.u64 b2, %3, 4;\n\t"
+      "add.u64 b3, %3, 6;\n\t"
+      "add.u64 b4, %3, bs;\n\t"
+      "add.u64 b5, b4, 2;\n\t"
+      "add.u64 b6, b4, 4;\n\t"
+      "add.u64 b7, b4, 6;\n\t"
+      "@pskip bra SKIP_MMA_%=;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [%2], %3, %5, pacc;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [a1], b1, %5, pone;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [a2], b2, %5, pone;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [a3], b3, %5, pone;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [a4], b4, %5, pone;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [a5], b5, %5, pone;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [a6], b6, %5, pone;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [a7], b7, %5, pone;\n\t"
+      "SKIP_MMA_%=:\n\t"
+      "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%7];\n\t"
+      "and.pred pna, pna, pnx;\n\t"
+      "selp.u32 %0, 1, 0, pna;\n\t"
+      "}"
+      : "=r"(ok)
+      : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(box_step), "r"(idesc), "r"(acc0), "r"(commit_bar), "r"(next_bar_a),
+        "r"(next_par_a), "r"(next_bar_x), "r"(next_par_x), "r"(static_cast<uint32_t>(skip_mma))
+      : "memory");
+  return ok != 0;
+}
+
 // D[tmem] (+)= A[smem desc] * B[smem desc]
 HM_DEVICE void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                           uint32_t accumulate) {

@@ -1,0 +1,119 @@
+"""Regenerates the golden fixtures in this directory from the reference itself.
+
+Run in a container where the reference tree is mounted (default /root/reference)
+and oracle/_ref has been built (sh oracle/build_ref.sh):
+
+    python tests/golden/make_golden.py
+
+What is executed from the reference, unmodified:
+  * humming.dtypes (pure Python)                                -> dtypes.json
+  * humming.utils.test.generate_random_moe_tensors, with torch's
+    factory functions redirected from "cuda:0" to the CPU       -> moe_align.npz
+  * pack_weight_kernel / unpack_weight_kernel / dequant_unpacked_fp_type,
+    the reference's CUDA kernel bodies compiled for the host
+    (oracle/ref_host.cpp)                                       -> pack_bits.npz, decode_fp.npz
+The reference has no fixtures of its own; these files are the pinned vectors
+the CPU oracle is checked against wherever the reference tree is absent.
+"""
+import ctypes
+import json
+import os
+import sys
+from unittest import mock
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+REF = os.environ.get("REF", "/root/reference")
+sys.path.insert(0, REF)
+
+
+def golden_dtypes():
+    from humming import dtypes as ref
+
+    names = ["uint1", "uint2", "uint3", "uint4", "uint5", "uint6", "uint7", "uint8", "int2", "int3", "int4", "int6", "int8",
+             "int32", "float4e2m1", "float6e2m3", "float6e3m2", "float8e4m3", "float8e5m2", "float8e8m0", "float16",
+             "bfloat16", "float32", "half", "float8_e4m3", "UINT4"]
+    out = {}
+    for n in names:
+        try:
+            d = ref.DataType.from_str(n)
+        except Exception as exc:  # error behaviour is part of the interface
+            out[n] = {"error": type(exc).__name__}
+            continue
+        rec = {"str": str(d), "upper": d.to_str(lowercase=False), "cpp": d.to_cpp_str(), "num_bits": d.num_bits,
+               "is_signed": bool(d.is_signed), "is_integer": bool(d.is_integer_type), "id": d.id()}
+        if d.is_floating_point_type:
+            rec.update(exponent_bits=d.exponent_bits, mantissa_bits=d.mantissa_bits)
+        out[n] = rec
+    out["__torch_map__"] = {str(k): str(v) for k, v in ref.torch_dtype_map.items()}
+    out["__from_torch__"] = {}
+    for t in (torch.float16, torch.bfloat16, torch.float32, torch.float8_e4m3fn, torch.float8_e5m2, torch.int8, torch.int32):
+        try:
+            out["__from_torch__"][str(t)] = str(ref.DataType.from_torch_dtype(t))
+        except Exception as exc:
+            out["__from_torch__"][str(t)] = "error:" + type(exc).__name__
+    with open(os.path.join(HERE, "dtypes.json"), "w") as f:
+        json.dump(out, f, indent=1, sort_keys=True)
+
+
+def golden_moe_align():
+    def cpu(fn):
+        def wrapped(*a, **k):
+            k.pop("device", None)
+            return fn(*a, **k)
+        return wrapped
+
+    with mock.patch("torch.randn", cpu(torch.randn)), mock.patch("torch.tensor", cpu(torch.tensor)):
+        # the reference module imports its CUDA kernel wrappers at import time; they are not called here
+        from humming.utils.test import generate_random_moe_tensors
+
+        cases = {}
+        for i, (m, e, k, blk) in enumerate([(1, 4, 2, 32), (18, 19, 3, 32), (512, 4, 2, 32), (64, 128, 8, 16), (7, 8, 8, 16)]):
+            torch.manual_seed(100 + i)
+            topk_ids, topk_w, sorted_ids, expert_ids, ntpp = generate_random_moe_tensors(m, e, k, blk)
+            cases[f"c{i}_shape"] = np.array([m, e, k, blk])
+            cases[f"c{i}_topk_ids"] = topk_ids.numpy()
+            cases[f"c{i}_sorted_token_ids"] = sorted_ids.numpy()
+            cases[f"c{i}_expert_ids"] = expert_ids.numpy()
+            cases[f"c{i}_num_tokens_post_padded"] = np.array(int(ntpp))
+    np.savez_compressed(os.path.join(HERE, "moe_align.npz"), **cases)
+
+
+def golden_host_kernels():
+    lib = ctypes.CDLL(os.path.join(ROOT, "oracle", "_ref", "libhumming_ref_host.so"))
+    rng = np.random.default_rng(2024)
+    pack = {}
+    for bits in range(1, 9):
+        codes = rng.integers(0, 1 << bits, size=2048, dtype=np.uint32)
+        packed = np.zeros(2048 * bits // 32, dtype=np.uint32)
+        assert lib.ref_pack_weight(codes.ctypes.data_as(ctypes.c_void_p), packed.ctypes.data_as(ctypes.c_void_p),
+                                   ctypes.c_long(2048), bits) == 0
+        back = np.zeros(2048, dtype=np.uint32)
+        assert lib.ref_unpack_weight(packed.ctypes.data_as(ctypes.c_void_p), back.ctypes.data_as(ctypes.c_void_p),
+                                     ctypes.c_long(2048), bits) == 0
+        assert np.array_equal(back, codes)
+        pack[f"codes{bits}"] = codes
+        pack[f"packed{bits}"] = packed
+    np.savez_compressed(os.path.join(HERE, "pack_bits.npz"), **pack)
+
+    dec = {}
+    for name, (e, m, signed) in {"e2m1": (2, 1, 1), "e4m3": (4, 3, 1), "e5m2": (5, 2, 1), "e3m2": (3, 2, 1), "e2m3": (2, 3, 1),
+                                 "e8m0": (8, 0, 0), "e3m4": (3, 4, 1)}.items():
+        nbits = e + m + signed
+        codes = np.arange(1 << nbits, dtype=np.uint32)
+        out = np.zeros(codes.size, dtype=np.float32)
+        assert lib.ref_dequant_fp(codes.ctypes.data_as(ctypes.c_void_p), out.ctypes.data_as(ctypes.c_void_p),
+                                  ctypes.c_long(codes.size), e, m, signed) == 0
+        dec[name] = out
+        dec[name + "_fmt"] = np.array([e, m, signed])
+    np.savez_compressed(os.path.join(HERE, "decode_fp.npz"), **dec)
+
+
+if __name__ == "__main__":
+    golden_dtypes()
+    golden_host_kernels()
+    golden_moe_align()
+    print("golden fixtures written to", HERE)

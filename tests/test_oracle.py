@@ -1,0 +1,178 @@
+"""CPU tests that pin the oracle: against the committed golden vectors (made by
+tests/golden/make_golden.py from the reference itself) and, where the host
+build of the reference's kernels is present (oracle/_ref), against that code
+directly.  Also checks the host-side mirror of the reference interface
+(dtypes, layer metadata, generators) that needs no GPU."""
+import ctypes
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import oracle
+from humming_b200 import dtypes
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+GOLD = os.path.join(HERE, "golden")
+REF_LIB = os.path.join(os.path.dirname(HERE), "oracle", "_ref", "libhumming_ref_host.so")
+
+
+# ---------------------------------------------------------------- bit packing
+@pytest.mark.parametrize("bits", range(1, 9))
+def test_pack_unpack_match_golden(bits):
+    g = np.load(os.path.join(GOLD, "pack_bits.npz"))
+    codes, packed = g[f"codes{bits}"], g[f"packed{bits}"]
+    assert np.array_equal(oracle.pack_bits(codes, bits), packed)
+    assert np.array_equal(oracle.unpack_bits(packed, bits), codes)
+
+
+@pytest.mark.skipif(not os.path.exists(REF_LIB), reason="host build of the reference kernels not present")
+@pytest.mark.parametrize("bits", range(1, 9))
+def test_pack_unpack_match_reference_code(bits):
+    lib = ctypes.CDLL(REF_LIB)
+    rng = np.random.default_rng(bits + 50)
+    codes = rng.integers(0, 1 << bits, size=4096, dtype=np.uint32)
+    packed = np.zeros(4096 * bits // 32, dtype=np.uint32)
+    assert lib.ref_pack_weight(codes.ctypes.data_as(ctypes.c_void_p), packed.ctypes.data_as(ctypes.c_void_p), ctypes.c_long(4096), bits) == 0
+    assert np.array_equal(oracle.pack_bits(codes, bits), packed)
+    back = np.zeros(4096, dtype=np.uint32)
+    assert lib.ref_unpack_weight(packed.ctypes.data_as(ctypes.c_void_p), back.ctypes.data_as(ctypes.c_void_p), ctypes.c_long(4096), bits) == 0
+    assert np.array_equal(oracle.unpack_bits(packed, bits), back)
+
+
+def test_pack_four_bit_layout_is_little_endian_nibbles():
+    codes = np.arange(32, dtype=np.uint32) % 16
+    words = oracle.pack_bits(codes, 4)
+    assert words.tolist() == [0x76543210, 0xFEDCBA98, 0x76543210, 0xFEDCBA98]
+
+
+# ---------------------------------------------------------------- float decode
+def test_decode_fp_matches_golden():
+    g = np.load(os.path.join(GOLD, "decode_fp.npz"))
+    for name in ("e2m1", "e4m3", "e5m2", "e3m2", "e2m3", "e8m0", "e3m4"):
+        e, m, signed = (int(v) for v in g[name + "_fmt"])
+        codes = np.arange(1 << (e + m + signed), dtype=np.uint32)
+        got = oracle.decode_fp(codes, e, m, bool(signed))
+        assert np.array_equal(got.view(np.uint32), g[name].view(np.uint32)), name
+
+
+def test_decode_fp_known_values():
+    e2m1 = oracle.decode_fp(np.arange(16), 2, 1, True)
+    assert e2m1.tolist() == [0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0]
+    # finite e4m3 codes agree with torch's e4m3fn decoding (the reference decodes 0x7F as a number, torch as NaN)
+    codes = np.array([c for c in range(256) if (c & 0x7F) != 0x7F], dtype=np.uint8)
+    want = torch.from_numpy(codes).view(torch.float8_e4m3fn).float().numpy()
+    assert np.array_equal(oracle.decode_fp(codes, 4, 3, True), want)
+    assert np.array_equal(oracle.e8m0_to_float(np.array([127, 119, 125])), np.array([1.0, 2.0 ** -8, 0.25], dtype=np.float32))
+
+
+def test_round_to_bf16_matches_torch():
+    x = np.random.default_rng(0).standard_normal(10000).astype(np.float32) * 37.0
+    assert np.array_equal(oracle.round_to_bf16(x), torch.from_numpy(x).bfloat16().float().numpy())
+    assert np.array_equal(oracle.round_to_16(x, "float16"), torch.from_numpy(x).half().float().numpy())
+
+
+# ---------------------------------------------------------------- weights
+def test_weight_ref_int_is_exact_and_matches_torch_expression():
+    rng = np.random.default_rng(1)
+    q = rng.integers(0, 16, size=(64, 256)).astype(np.int32)
+    zp = rng.integers(0, 16, size=(64, 2)).astype(np.int32)
+    s = (np.abs(rng.standard_normal((64, 2))) * 0.02 + 1e-3).astype(np.float32)
+    s = torch.from_numpy(s).bfloat16().float().numpy()
+    got = oracle.weight_ref_int(q, s, 128, 4, zp)
+    # the reference's expression (humming/utils/test.py:109-128) on CPU tensors
+    tq, tz, ts = torch.from_numpy(q), torch.from_numpy(zp), torch.from_numpy(s)
+    want = (tq.float() - tz.repeat_interleave(128, -1)) * ts.float().repeat_interleave(128, -1)
+    assert np.array_equal(got, want.numpy())
+    sym = oracle.weight_ref_int(q, s, 128, 4, None)
+    assert np.array_equal(sym, ((tq.float() - 8) * ts.repeat_interleave(128, -1)).numpy())
+    # one rounding to the activation type is what the kernels multiply by
+    eff = oracle.effective_weight_16(got, "bfloat16")
+    assert np.array_equal(eff, want.bfloat16().float().numpy())
+
+
+@pytest.mark.parametrize("zp", [False, True])
+def test_quantize_weight_round_trip_error_bound(zp):
+    rng = np.random.default_rng(5)
+    w = rng.standard_normal((32, 512)).astype(np.float32)
+    q, s, z = oracle.quantize_weight_int(w, 4, 128, zp)
+    assert q.min() >= 0 and q.max() <= 15
+    ref = oracle.weight_ref_int(q, s, 128, 4, z)
+    step = np.repeat(np.abs(s), 128, axis=-1)
+    assert np.all(np.abs(ref - w) <= 0.5001 * step + 1e-6)
+
+
+# ---------------------------------------------------------------- MoE alignment
+def test_moe_align_matches_golden():
+    g = np.load(os.path.join(GOLD, "moe_align.npz"))
+    for i in range(5):
+        m, e, k, blk = (int(v) for v in g[f"c{i}_shape"])
+        sorted_ids, expert_ids, total = oracle.moe_align_block_size(g[f"c{i}_topk_ids"], e, blk)
+        assert np.array_equal(sorted_ids, g[f"c{i}_sorted_token_ids"])
+        assert np.array_equal(expert_ids, g[f"c{i}_expert_ids"])
+        assert int(total) == int(g[f"c{i}_num_tokens_post_padded"])
+        assert sorted_ids.size % blk == 0 and (sorted_ids < m * k).sum() == m * k
+
+
+# ---------------------------------------------------------------- host-side mirror of the reference interface
+def test_dtypes_match_reference_golden():
+    gold = json.load(open(os.path.join(GOLD, "dtypes.json")))
+    for name, rec in gold.items():
+        if name.startswith("__"):
+            continue
+        if "error" in rec:
+            with pytest.raises(Exception) as exc:
+                dtypes.DataType.from_str(name)
+            assert type(exc.value).__name__ == rec["error"], name
+            continue
+        d = dtypes.DataType.from_str(name)
+        assert str(d) == rec["str"] and d.to_str(lowercase=False) == rec["upper"] and d.to_cpp_str() == rec["cpp"]
+        assert d.num_bits == rec["num_bits"] and bool(d.is_signed) == rec["is_signed"] and d.id() == rec["id"]
+        assert d.is_integer_type == rec["is_integer"] and d.is_floating_point_type == (not rec["is_integer"])
+        if not rec["is_integer"]:
+            assert d.exponent_bits == rec["exponent_bits"] and d.mantissa_bits == rec["mantissa_bits"]
+    for k, v in gold["__torch_map__"].items():
+        assert str(dtypes.torch_dtype_map[dtypes.DataType.from_str(k)]) == v
+    for t in (torch.float16, torch.bfloat16, torch.float32, torch.float8_e4m3fn, torch.float8_e5m2, torch.int8, torch.int32):
+        assert str(dtypes.DataType.from_torch_dtype(t)) == gold["__from_torch__"][str(t)]
+    assert dtypes.uint4 == dtypes.DataType.from_str("uint4") and hash(dtypes.uint4) == hash("uint4")
+
+
+def test_layer_meta_and_parameter_shapes_follow_the_reference():
+    from humming_b200.layer import HummingLayer, HummingLayerMeta
+
+    meta = HummingLayerMeta(a_dtype="bfloat16", b_dtype="uint4", c_dtype="bfloat16", bs_dtype="bfloat16", shape_n=4096,
+                            shape_k=14336, weight_scale_group_size=128, has_dynamic_zp=True, has_bias=True, sublayer_name="down")
+    assert meta.weight_name == "down_weight" and meta.zero_point_name == "down_zero_point" and meta.has_input_scale is None
+    layer = HummingLayer(shape_n=1024, shape_k=1024, a_dtype=dtypes.float16, b_dtype=dtypes.uint4, c_dtype=dtypes.float16,
+                         bs_dtype=dtypes.float16, weight_scale_group_size=128, has_dynamic_zp=True, has_bias=True)
+    # reference humming/layer.py:110-158: weight (K/16, N*2), scales (K/g, N), zero points (K/g, N/8), bias (N,), locks 1024
+    assert tuple(layer.weight.shape) == (64, 2048) and layer.weight.dtype == torch.int32
+    assert tuple(layer.weight_scale.shape) == (8, 1024) and layer.weight_scale.dtype == torch.float16
+    assert tuple(layer.zero_point.shape) == (8, 128) and tuple(layer.bias.shape) == (1024,)
+    assert tuple(layer.locks.shape) == (1024,) and not layer.weight.requires_grad
+    moe = HummingLayer(shape_n=1536, shape_k=2048, a_dtype="bfloat16", b_dtype="uint4", c_dtype="bfloat16", bs_dtype="bfloat16",
+                       weight_scale_group_size=128, num_experts=4)
+    assert tuple(moe.weight.shape) == (4, 128, 3072) and tuple(moe.weight_scale.shape) == (4, 16, 1536)
+    with pytest.raises(NotImplementedError):
+        HummingLayer(shape_n=1024, shape_k=1024, a_dtype="float16", b_dtype="uint3", c_dtype="float16", bs_dtype="float16")
+    with pytest.raises(NotImplementedError):
+        HummingLayer(shape_n=1000, shape_k=1024, a_dtype="float16", b_dtype="uint4", c_dtype="float16", bs_dtype="float16")
+    with pytest.raises(ValueError):
+        HummingLayer(shape_n=1024, shape_k=1024, a_dtype="float16", b_dtype="int4", c_dtype="float16", bs_dtype="float16",
+                     has_dynamic_zp=True)
+    with pytest.raises(RuntimeError):
+        layer(inputs=torch.zeros(1, 1024, dtype=torch.float16))  # finish_load not called
+
+
+def test_synthetic_cases_are_seeded_and_match_the_oracle_expression():
+    from humming_b200.utils import synthetic
+
+    a = synthetic.dense_w4a16_case(256, 512, torch.bfloat16, True, seed=3)
+    b = synthetic.dense_w4a16_case(256, 512, torch.bfloat16, True, seed=3)
+    assert torch.equal(a.codes, b.codes) and torch.equal(a.scales, b.scales) and torch.equal(a.zero_points, b.zero_points)
+    assert int(a.codes.min()) >= 0 and int(a.codes.max()) <= 15 and float(a.scales.float().min()) > 0
+    want = oracle.weight_ref_int(a.codes.numpy(), a.scales.float().numpy(), 128, 4, a.zero_points.numpy())
+    assert np.array_equal(a.weight_ref().numpy(), want)

@@ -167,6 +167,39 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def run_point(args):
+    """`--point PROJ:M`: a few eager launches of one sweep point (used for ncu captures)."""
+    from humming_b200.layer import HummingLayer
+    from humming_b200.utils import synthetic
+
+    name, m = args.point.split(":")
+    m = int(m)
+    n, k = synthetic.LLAMA3_8B_SHAPES[name]
+    dev = torch.device("cuda", 0)
+    case = synthetic.dense_w4a16_case(n, k, torch.bfloat16, True, seed=0)
+    layers = []
+    for _ in range(N_COPIES):
+        layer = HummingLayer(shape_n=n, shape_k=k, a_dtype="bfloat16", b_dtype="uint4", c_dtype="bfloat16",
+                             bs_dtype="bfloat16", weight_scale_group_size=GROUP, has_dynamic_zp=True).to(dev)
+        layer.load_weight(weight=case.codes.to(dev), weight_scale=case.scales.to(dev), zero_point=case.zero_points.to(dev))
+        layer.finish_load()
+        layers.append(layer)
+    x = synthetic.activations(m, k, torch.bfloat16).to(dev)
+    out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+    us = []
+    for r in range(max(args.steps, 1) + max(args.warmup, 0)):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        layers[r % N_COPIES](inputs=x, outputs=out)
+        e1.record()
+        torch.cuda.synchronize()
+        us.append(e0.elapsed_time(e1) * 1e3)
+    for layer in layers:
+        layer.check_status()
+    print(json.dumps({"point": args.point, "launch_us_including_host_gap": [round(v, 1) for v in us],
+                      "algorithmic_bytes": gemm_bytes(m, n, k), "flops": gemm_flops(m, n, k)}), flush=True)
+
+
 def run_ours(args, rank, world, local_rank):
     import torch.distributed as dist
     from humming_b200 import runtime
@@ -341,6 +374,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--point", default=None, help="PROJ:M, e.g. gate_up:16 -- launch only this sweep point a few times")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -348,6 +382,9 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.point:
+        run_point(args)
         return
     if world > 1:
         import torch.distributed as dist

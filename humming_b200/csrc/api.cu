@@ -383,6 +383,7 @@ int hm_gemm(const hm_gemm_desc* desc, int64_t m, const void* a, int64_t lda, con
 
   const int g = desc->group_size == 0 ? desc->shape_k : desc->group_size;
   hm::GemmParams p;
+  memset(&p, 0, sizeof(p));
   p.w = static_cast<const uint8_t*>(w);
   p.w_scale = static_cast<const uint8_t*>(w_scale);
   p.w_zp = static_cast<const uint8_t*>(w_zp);
@@ -416,6 +417,178 @@ int hm_gemm(const hm_gemm_desc* desc, int64_t m, const void* a, int64_t lda, con
     case 256: return dispatch_gemm<256>(bf16, desc->has_zp != 0, a_tmem, p, tmap, pl.grid, s);
   }
   return fail(HM_ERR_INVALID, "no kernel for m_tile=%d", pl.m_tile);
+}
+
+// ---- MoE -------------------------------------------------------------------------
+extern "C++" {
+namespace {
+
+int validate_moe(const hm_gemm_desc* d, int64_t capacity, int* mt_out) {
+  if (d == nullptr) return fail(HM_ERR_INVALID, "desc is NULL");
+  hm_gemm_desc tmp = *d;
+  tmp.num_experts = 0;
+  tmp.m_tile = 0;
+  int rc = validate_desc(&tmp);
+  if (rc != HM_OK) return rc;
+  if (d->num_experts <= 0) return fail(HM_ERR_INVALID, "hm_moe_gemm needs num_experts > 0");
+  if (d->top_k <= 0) return fail(HM_ERR_INVALID, "top_k must be positive");
+  const int mt = d->m_tile;
+  if (mt != 16 && mt != 32 && mt != 64 && mt != 128)
+    return fail(HM_ERR_INVALID, "MoE token tile (m_tile = alignment block) must be 16, 32, 64 or 128, got %d", mt);
+  if (d->flags & HM_FLAG_A_OPERAND_SMEM) return fail(HM_ERR_UNSUPPORTED, "MoE has no shared-memory operand variant");
+  if (capacity <= 0 || capacity % mt != 0 || capacity > (1ll << 30))
+    return fail(HM_ERR_INVALID, "sorted_ids capacity %lld must be a positive multiple of the token tile %d",
+                static_cast<long long>(capacity), mt);
+  const int64_t units = capacity / mt * (d->shape_n / hm::kTileN) * (d->shape_k / hm::kStageK);
+  if (units >= (1ll << 31)) return fail(HM_ERR_INVALID, "problem too large for 32-bit unit indices");
+  *mt_out = mt;
+  return HM_OK;
+}
+
+int64_t moe_workspace_bytes(const hm_gemm_desc* d, int64_t capacity, int mt, int sms) {
+  const int64_t tiles = capacity / mt * (d->shape_n / hm::kTileN);
+  const int64_t counters = ((tiles * 16 + 255) / 256) * 256;
+  return 256 + counters + static_cast<int64_t>(sms) * 2 * mt * hm::kTileN * 4;
+}
+
+template <int MT, bool BF16, bool HAS_ZP>
+int launch_moe(const hm::GemmParams& p, int grid, cudaStream_t stream) {
+  using Cfg = hm::GemmCfg<MT, true>;
+  auto kern = hm::gemm_w4a16_kernel<MT, BF16, HAS_ZP, true, true>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  HM_CUDA_OK(cudaGetDevice(&dev));
+  if (!configured[dev & 63]) {
+    HM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_ALLOC));
+    configured[dev & 63] = true;
+  }
+  CUtensorMap unused;
+  memset(&unused, 0, sizeof(unused));
+  kern<<<grid, Cfg::THREADS, Cfg::SMEM_ALLOC, stream>>>(p, unused);
+  HM_CUDA_OK(cudaGetLastError());
+  return HM_OK;
+}
+
+template <int MT>
+int dispatch_moe(bool bf16, bool zp, const hm::GemmParams& p, int grid, cudaStream_t stream) {
+  if (bf16) return zp ? launch_moe<MT, true, true>(p, grid, stream) : launch_moe<MT, true, false>(p, grid, stream);
+  return zp ? launch_moe<MT, false, true>(p, grid, stream) : launch_moe<MT, false, false>(p, grid, stream);
+}
+
+}  // namespace
+}  // extern "C++"
+
+int hm_moe_align_block_size(const int32_t* topk_ids, int64_t numel, int num_experts, int block, int32_t* sorted_ids,
+                            int64_t capacity, int32_t* expert_ids, int32_t* num_post_padded, int32_t* scratch,
+                            void* stream) {
+  if (topk_ids == nullptr || sorted_ids == nullptr || expert_ids == nullptr || num_post_padded == nullptr || scratch == nullptr)
+    return fail(HM_ERR_INVALID, "NULL pointer");
+  if (numel <= 0 || numel > (1ll << 30) || num_experts <= 0 || num_experts > 65536 || block <= 0)
+    return fail(HM_ERR_INVALID, "bad numel / num_experts / block");
+  const int64_t need = ((numel + static_cast<int64_t>(num_experts) * (block - 1) + block - 1) / block) * block;
+  if (capacity % block != 0 || capacity < need)
+    return fail(HM_ERR_INVALID, "sorted_ids capacity %lld too small: %lld needed (numel + experts * (block - 1), rounded up to the block)",
+                static_cast<long long>(capacity), static_cast<long long>(need));
+  auto s = static_cast<cudaStream_t>(stream);
+  int* counts = scratch;
+  int* offsets = scratch + num_experts;
+  HM_CUDA_OK(cudaMemsetAsync(counts, 0, sizeof(int) * num_experts, s));
+  HM_CUDA_OK(cudaMemsetAsync(expert_ids, 0, sizeof(int) * (capacity / block), s));
+  hm::moe_count_kernel<<<blocks_for(numel, 256), 256, 0, s>>>(topk_ids, static_cast<int>(numel), num_experts, counts);
+  hm::moe_scan_kernel<<<1, 1024, 0, s>>>(counts, num_experts, block, static_cast<int>(numel), static_cast<int>(capacity),
+                                         offsets, expert_ids, num_post_padded, sorted_ids);
+  hm::moe_scatter_kernel<<<(num_experts + 7) / 8, 256, 0, s>>>(topk_ids, static_cast<int>(numel), num_experts, offsets, sorted_ids);
+  HM_CUDA_OK(cudaGetLastError());
+  return HM_OK;
+}
+
+size_t hm_moe_gemm_workspace_bytes(const hm_gemm_desc* desc, int64_t capacity) {
+  int mt = 0;
+  if (validate_moe(desc, capacity, &mt) != HM_OK) return 0;
+  int sms = desc->num_sms;
+  if (sms <= 0 && device_sm_count(&sms) != HM_OK) return 0;
+  return static_cast<size_t>(moe_workspace_bytes(desc, capacity, mt, sms));
+}
+
+int hm_moe_gemm(const hm_gemm_desc* desc, int64_t num_valid, const void* a, int64_t lda, const void* w,
+                const void* w_scale, const void* w_zp, const void* bias, const float* topk_weights,
+                const int32_t* sorted_ids, int64_t capacity, const int32_t* expert_ids,
+                const int32_t* num_post_padded, void* c, int64_t ldc, void* workspace, size_t workspace_bytes,
+                void* stream) {
+  int mt = 0;
+  int rc = validate_moe(desc, capacity, &mt);
+  if (rc != HM_OK) return rc;
+  if (num_valid == 0) return HM_OK;
+  if (num_valid < 0 || num_valid > (1ll << 30) || num_valid % desc->top_k != 0)
+    return fail(HM_ERR_INVALID, "num_valid=%lld must be tokens * top_k", static_cast<long long>(num_valid));
+  if (a == nullptr || w == nullptr || w_scale == nullptr || c == nullptr || sorted_ids == nullptr || expert_ids == nullptr ||
+      num_post_padded == nullptr)
+    return fail(HM_ERR_INVALID, "NULL pointer");
+  if (desc->has_zp && w_zp == nullptr) return fail(HM_ERR_INVALID, "w_zp is NULL but the descriptor has zero points");
+  if (desc->has_bias && bias == nullptr) return fail(HM_ERR_INVALID, "bias is NULL but the descriptor has a bias");
+  if (desc->is_moe_down && topk_weights == nullptr) return fail(HM_ERR_INVALID, "the down projection needs topk_weights");
+  if (lda < desc->shape_k || ldc < desc->shape_n) return fail(HM_ERR_INVALID, "lda/ldc smaller than the row length");
+  if ((reinterpret_cast<uintptr_t>(a) & 15) || (lda & 7) || (reinterpret_cast<uintptr_t>(c) & 15) || (ldc & 7))
+    return fail(HM_ERR_INVALID, "activations and output must be 16-byte aligned with 16-byte row pitches");
+  if ((reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(w_scale) & 15) || (reinterpret_cast<uintptr_t>(w_zp) & 15))
+    return fail(HM_ERR_INVALID, "prepared weight buffers must be 16-byte aligned");
+  int sms = desc->num_sms;
+  if (sms <= 0) {
+    rc = device_sm_count(&sms);
+    if (rc != HM_OK) return rc;
+  }
+  const int64_t need = moe_workspace_bytes(desc, capacity, mt, sms);
+  if (workspace == nullptr || workspace_bytes < static_cast<size_t>(need))
+    return fail(HM_ERR_WORKSPACE, "workspace of %zu bytes given, %lld needed", workspace_bytes, static_cast<long long>(need));
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return fail(HM_ERR_INVALID, "workspace must be 256-byte aligned");
+
+  const int g = desc->group_size == 0 ? desc->shape_k : desc->group_size;
+  hm::GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.w = static_cast<const uint8_t*>(w);
+  p.w_scale = static_cast<const uint8_t*>(w_scale);
+  p.w_zp = static_cast<const uint8_t*>(w_zp);
+  p.bias = desc->has_bias ? bias : nullptr;
+  p.c = c;
+  auto ws = static_cast<uint8_t*>(workspace);
+  p.status = reinterpret_cast<int*>(ws);
+  p.counters = reinterpret_cast<int*>(ws + 256);
+  const int64_t tiles = capacity / mt * (desc->shape_n / hm::kTileN);
+  p.partials = reinterpret_cast<float*>(ws + 256 + ((tiles * 16 + 255) / 256) * 256);
+  p.M = static_cast<int>(num_valid);
+  p.N = desc->shape_n;
+  p.K = desc->shape_k;
+  p.ldc = static_cast<int>(ldc);
+  p.groups = desc->shape_k / g;
+  p.steps_per_group = g >= hm::kStageK ? g / hm::kStageK : 1;
+  p.groups_per_step = g >= hm::kStageK ? 1 : hm::kStageK / g;
+  p.sched.n_tiles = desc->shape_n / hm::kTileN;
+  p.sched.kb_per_tile = desc->shape_k / hm::kStageK;
+  p.sched.m_tiles = static_cast<int>(capacity / mt);
+  p.sched.mode = 1;
+  p.sched.grid = sms;
+  p.trace = g_trace;
+  p.dbg = g_dbg;
+  p.a = a;
+  p.lda = static_cast<int>(lda);
+  p.sorted_ids = sorted_ids;
+  p.expert_ids = expert_ids;
+  p.num_post_padded = num_post_padded;
+  p.topk_weights = topk_weights;
+  p.top_k = desc->top_k;
+  p.is_down = desc->is_moe_down ? 1 : 0;
+  p.num_valid = static_cast<int>(num_valid);
+  p.max_m_tiles = static_cast<int>(capacity / mt);
+  p.min_units = 2;
+  const bool bf16 = desc->a_dtype == HM_BF16;
+  auto s = static_cast<cudaStream_t>(stream);
+  switch (mt) {
+    case 16: return dispatch_moe<16>(bf16, desc->has_zp != 0, p, sms, s);
+    case 32: return dispatch_moe<32>(bf16, desc->has_zp != 0, p, sms, s);
+    case 64: return dispatch_moe<64>(bf16, desc->has_zp != 0, p, sms, s);
+    case 128: return dispatch_moe<128>(bf16, desc->has_zp != 0, p, sms, s);
+  }
+  return fail(HM_ERR_INVALID, "no MoE kernel for token tile %d", mt);
 }
 
 // ---- hm_gemm_static_scratch ------------------------------------------------------

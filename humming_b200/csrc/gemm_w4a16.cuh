@@ -75,6 +75,18 @@ struct GemmParams {
   SchedParams sched;       // units are 128-K steps
   unsigned long long* trace;  // debug: per-role clock64 timeline of CTA 0, or null
   int dbg;                    // debug: HM_DBG_* experiment switches (0 in production)
+  // ---- indexed (MoE) GEMM only ----
+  const void* a;               // activations [rows, lda] (gathered by id)
+  int lda;
+  const int* sorted_ids;       // flat (token, slot) ids grouped by expert, padded per expert to a multiple of the token tile
+  const int* expert_ids;       // expert of each token-tile-sized block of sorted_ids
+  const int* num_post_padded;  // device scalar: used length of sorted_ids
+  const float* topk_weights;   // [num_valid] (down projection) or null
+  int top_k;
+  int is_down;                 // 1: read row = id and scale by topk_weights[id]; 0: read row = id / top_k
+  int num_valid;               // tokens * top_k; ids >= num_valid are padding
+  int max_m_tiles;             // capacity of sorted_ids in token tiles
+  int min_units;               // smallest K-split worth a CTA
 };
 
 template <int MT, bool A_TMEM>
@@ -112,7 +124,7 @@ struct GemmCfg {
   static constexpr int SMEM_A = SMEM_X + SX * X_STAGE;
   static constexpr int SMEM_W = SMEM_A + SA * A_STAGE;
   static constexpr int SMEM_STAGE = SMEM_W + SW * kWStageBytes;  // epilogue transpose staging, 2 KB per warp
-  static constexpr int SMEM_BAR = SMEM_STAGE + 4 * 2048;
+  static constexpr int SMEM_BAR = SMEM_STAGE + 4 * 2048 + 1024;  // + gathered-row indices of the MoE producer
   static constexpr int SMEM_TOTAL = SMEM_BAR + kNumBarrierSlots * 8 + 64;
   static constexpr int SMEM_ALLOC = SMEM_TOTAL + 1024;  // slack for manual 1024-byte alignment
   static_assert(USED_COLS <= 512, "tensor memory budget");
@@ -164,7 +176,16 @@ struct Ring {
   }
 };
 
-template <int MT, bool BF16, bool HAS_ZP, bool A_TMEM>
+// MOE = true: the indexed GEMM of the reference's MoE mode
+// (humming/include/humming/scheduler.cuh:158-182,
+// memory/g2s_loader/loader_a.cuh:76-91, epilogue/gmem_writer.cuh:169-192):
+// token tiles are blocks of sorted_ids, each block belongs to one expert, the
+// activation rows are gathered by id (cp.async by the whole producer warp, in
+// the same swizzled layout a TMA box would write), output rows are scattered
+// by id and the down projection multiplies by the routing weight.  The number
+// of token tiles is a device scalar, so the K-split schedule is derived on the
+// device.
+template <int MT, bool BF16, bool HAS_ZP, bool A_TMEM, bool MOE = false>
 __global__ void __launch_bounds__(GemmCfg<MT, A_TMEM>::THREADS, 1)
 gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
   using Cfg = GemmCfg<MT, A_TMEM>;
@@ -224,15 +245,31 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_holder)), Cfg::TMEM_COLS);
     tmem_relinquish();
   }
-  if (warp == 1 && lane == 0) tma_prefetch_desc(&tmap_x);
+  if (!MOE && warp == 1 && lane == 0) tma_prefetch_desc(&tmap_x);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
+  SchedParams sched = p.sched;
+  if constexpr (MOE) {
+    int m_tiles = (*p.num_post_padded + MT - 1) / MT;
+    if (m_tiles > p.max_m_tiles) m_tiles = p.max_m_tiles;
+    sched.m_tiles = m_tiles;
+    sched.mode = 1;
+    sched.grid = gridDim.x;
+    sched.total_units = m_tiles * sched.n_tiles * sched.kb_per_tile;
+    int per = (sched.total_units + sched.grid - 1) / sched.grid;
+    if (per < p.min_units) per = p.min_units;
+    sched.units_per_cta = per;
+  }
   SegIter iter;
-  iter.init(p.sched, blockIdx.x);
+  iter.init(sched, blockIdx.x);
   Segment seg;
+  // Per-expert strides of the prepared buffers (MoE only).
+  const size_t expert_code_bytes = static_cast<size_t>(sched.n_tiles) * sched.kb_per_tile * (2 * kCodeBytes);
+  const size_t expert_groups = static_cast<size_t>(sched.n_tiles) * p.groups;
+  auto expert_of = [&](const Segment& s) -> size_t { return MOE ? static_cast<size_t>(p.expert_ids[s.m_tile]) : 0; };
   const bool tracing = p.trace != nullptr && blockIdx.x == 0;
   auto trace = [&](int role, int idx, int j) {
     if (tracing && idx < kTraceEvents) p.trace[(role * kTraceEvents + idx) * 4 + j] = clock64();
@@ -247,7 +284,8 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
       int it = 0;
       bool ok = true;
       while (ok && iter.next(seg)) {
-        const uint8_t* codes = p.w + (static_cast<size_t>(seg.n_tile) * p.sched.kb_per_tile + seg.kb0) * (2 * kCodeBytes);
+        const uint8_t* codes = p.w + (static_cast<size_t>(seg.n_tile) * sched.kb_per_tile + seg.kb0) * (2 * kCodeBytes) +
+                               expert_of(seg) * expert_code_bytes;
         for (int ks = seg.kb0; ks < seg.kb1; ++ks, ++it) {
           if (!mbar_wait_bounded(w_empty(ring.idx), ring.phase ^ 1, abort_flag)) {
             report_abort(p.status, HM_ABORT_W_EMPTY, it, ring.idx);
@@ -294,8 +332,9 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
           g = seg.kb0 / p.steps_per_group;
           cnt = seg.kb0 - g * p.steps_per_group;
         }
-        const uint8_t* scales = p.w_scale + (static_cast<size_t>(seg.n_tile) * p.groups + g) * kScaleBytes;
-        const uint8_t* zps = HAS_ZP ? p.w_zp + (static_cast<size_t>(seg.n_tile) * p.groups + g) * kZpBytes : nullptr;
+        const size_t grp0 = expert_of(seg) * expert_groups + static_cast<size_t>(seg.n_tile) * p.groups + g;
+        const uint8_t* scales = p.w_scale + grp0 * kScaleBytes;
+        const uint8_t* zps = HAS_ZP ? p.w_zp + grp0 * kZpBytes : nullptr;
         for (int ks = seg.kb0; ks < seg.kb1; ++ks, ++it) {
           if (!mbar_wait_bounded(w_empty(ring.idx), ring.phase ^ 1, abort_flag)) {
             report_abort(p.status, HM_ABORT_W_EMPTY, it, ring.idx);
@@ -328,6 +367,72 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
           mbar_wait_bounded(w_full(last_it % SW), (last_it / SW) & 1, abort_flag + 1);
         }
       }
+    }
+  } else if (warp == 1 && MOE) {
+    // ------------------------------------------------ activation producer, gathered rows (whole warp)
+    // 8 lanes copy the 128 bytes of one row's 64-K slice, 4 rows per instruction;
+    // 16-byte chunk c of row r lands at chunk (c ^ (r & 7)) of its 128-byte line,
+    // 8-row groups 1024 bytes apart -- the layout of a 128-byte-swizzled TMA box.
+    // Copies of a stage form one cp.async group; a stage is published (proxy
+    // fence + arrive) once its group has landed, SX-1 stages later.
+    int* xrow = reinterpret_cast<int*>(smem_gen + Cfg::SMEM_STAGE + 4 * 2048);  // source row per token of the tile
+    Ring<SX> ring;      // stage being filled
+    Ring<SX> publish;   // oldest stage not yet published
+    Ring<SA> done;
+    int it = 0, published = 0;
+    bool ok = true;
+    const int sub_row = lane >> 3, chunk = lane & 7;
+    while (ok && iter.next(seg)) {
+      __syncwarp();
+      for (int r = lane; r < MT; r += 32) {
+        const int id = p.sorted_ids[seg.m_tile * MT + r];
+        xrow[r] = id < p.num_valid ? (p.is_down ? id : id / p.top_k) : -1;
+      }
+      __syncwarp();
+      int col = seg.kb0 * kStageK;
+      for (int ks = seg.kb0; ks < seg.kb1; ++ks, ++it) {
+        if (it >= SX) {
+          if (!mbar_wait_bounded(a_empty(done.idx), done.phase, abort_flag)) {
+            if (lane == 0) report_abort(p.status, HM_ABORT_X_EMPTY, it, ring.idx);
+            ok = false;
+            break;
+          }
+          done.advance();
+        }
+        const uint32_t dst0 = x_smem + ring.idx * Cfg::X_STAGE;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+          for (int i = 0; i < MT / 4; ++i) {
+            const int r = i * 4 + sub_row;
+            const int src_row = xrow[r];
+            const uint8_t* src = static_cast<const uint8_t*>(p.a) +
+                                 (static_cast<size_t>(src_row < 0 ? 0 : src_row) * p.lda + col + h * kBlockK + chunk * 8) * 2;
+            const uint32_t dst = dst0 + h * Cfg::X_BOX + (r >> 3) * 1024 + (r & 7) * 128 + ((chunk ^ (r & 7)) * 16);
+            cp_async_16(dst, src, src_row < 0 ? 0u : 16u);
+          }
+        }
+        cp_async_commit();
+        col += kStageK;
+        ring.advance();
+        if (it - published >= SX - 1) {
+          cp_async_wait<SX - 1>();
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(x_full(publish.idx));
+          publish.advance();
+          ++published;
+        }
+      }
+    }
+    // Publish what is still in flight (also on the abort path, so nothing lands after exit).
+    cp_async_wait<0>();
+    fence_proxy_async_smem();
+    __syncwarp();
+    while (ok && published < it) {
+      if (lane == 0) mbar_arrive(x_full(publish.idx));
+      publish.advance();
+      ++published;
     }
   } else if (warp == 1) {
     // ------------------------------------------------ activation producer
@@ -551,8 +656,8 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
       if (q == 0 && lane == 0) trace(7, sc + 1, 0);
       const int n = seg.n_tile * kTileN + row;
       const int m0 = seg.m_tile * MT;
-      const int m_valid = (p.M - m0) < MT ? (p.M - m0) : MT;
-      const float bias = (p.bias != nullptr) ? load_bias<BF16>(p.bias, n) : 0.f;
+      const int m_valid = MOE ? MT : ((p.M - m0) < MT ? (p.M - m0) : MT);
+      const float bias = (p.bias != nullptr) ? load_bias<BF16>(p.bias, static_cast<int>(expert_of(seg)) * p.N + n) : 0.f;
       float* slot = p.partials + static_cast<size_t>(seg.slot) * (MT * kTileN);
       const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + b * MT;
       constexpr int CH = MT >= 32 ? 32 : 16;  // token columns per chunk
@@ -576,10 +681,17 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
           // Transpose through shared memory so that global stores are 16 bytes per
           // lane: lane = weight row writes one 16-bit value per token into the
           // staging tile; then 4 lanes cover the 64 bytes of one token's 32 rows.
+          int out_id = 0;      // MoE: output row of token column (c0 + lane)
+          float out_w = 1.f;   // MoE down projection: its routing weight
+          if constexpr (MOE) {
+            out_id = (lane < CH) ? p.sorted_ids[m0 + c0 + lane] : p.num_valid;
+            if (p.is_down && out_id < p.num_valid) out_w = p.topk_weights[out_id];
+          }
           __syncwarp();
 #pragma unroll
           for (int j = 0; j < CH; ++j) {
-            const float o = v[j] + bias;
+            float o = v[j] + bias;
+            if constexpr (MOE) o *= __shfl_sync(0xffffffffu, out_w, j);
             if constexpr (BF16) {
               reinterpret_cast<__nv_bfloat16*>(stage)[j * 32 + lane] = __float2bfloat16_rn(o);
             } else {
@@ -591,9 +703,15 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
 #pragma unroll
           for (int i = 0; i < CH / 8; ++i) {
             const int j = i * 8 + (lane >> 2);
-            if (c0 + j < m_valid) {
+            int out_row = m0 + c0 + j;
+            bool valid = c0 + j < m_valid;
+            if constexpr (MOE) {
+              out_row = __shfl_sync(0xffffffffu, out_id, j);
+              valid = out_row < p.num_valid;
+            }
+            if (valid) {
               const uint4 val = *reinterpret_cast<const uint4*>(stage + j * 64 + (lane & 3) * 16);
-              uint8_t* dst = static_cast<uint8_t*>(p.c) + (static_cast<size_t>(m0 + c0 + j) * p.ldc + n_base) * 2 + (lane & 3) * 16;
+              uint8_t* dst = static_cast<uint8_t*>(p.c) + (static_cast<size_t>(out_row) * p.ldc + n_base) * 2 + (lane & 3) * 16;
               *reinterpret_cast<uint4*>(dst) = val;
             }
           }
@@ -635,7 +753,7 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
             for (int jj = 0; jj < 8; ++jj) acc[jj] = 0.f;
             for (int cs = 0; cs < seg.nseg; ++cs) {
               const int cta = seg.first_cta + cs;
-              const float* src = p.partials + static_cast<size_t>(sched_slot(p.sched, cta, seg.tile)) * (MT * kTileN) +
+              const float* src = p.partials + static_cast<size_t>(sched_slot(sched, cta, seg.tile)) * (MT * kTileN) +
                                  j0 * kTileN + row;
               float v[8];
 #pragma unroll
@@ -645,7 +763,16 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
             }
 #pragma unroll
             for (int jj = 0; jj < 8; ++jj) {
-              if (j0 + jj < m_valid) store_out<BF16>(p.c, static_cast<size_t>(m0 + j0 + jj) * p.ldc + n, acc[jj] + bias);
+              if (j0 + jj < m_valid) {
+                int out_row = m0 + j0 + jj;
+                float o = acc[jj] + bias;
+                if constexpr (MOE) {
+                  out_row = p.sorted_ids[m0 + j0 + jj];
+                  if (out_row >= p.num_valid) continue;
+                  if (p.is_down) o *= p.topk_weights[out_row];
+                }
+                store_out<BF16>(p.c, static_cast<size_t>(out_row) * p.ldc + n, o);
+              }
             }
           }
         }

@@ -205,4 +205,50 @@ __global__ void quant_rowwise_e4m3_kernel(const T* __restrict__ x, int64_t ldx, 
   }
 }
 
+// ---- MoE block alignment (humming/utils/test.py:154-183 does this in a Python loop) ----
+// counts[e] = number of flat (token, slot) entries routed to expert e.
+__global__ void moe_count_kernel(const int* __restrict__ topk_ids, int numel, int num_experts, int* __restrict__ counts) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < numel) {
+    const int e = topk_ids[i];
+    if (e >= 0 && e < num_experts) atomicAdd(&counts[e], 1);
+  }
+}
+// One CTA: padded offsets per expert, expert id per block, total padded length;
+// fills sorted_ids with the sentinel `numel`.
+__global__ void moe_scan_kernel(const int* __restrict__ counts, int num_experts, int block, int numel, int capacity,
+                                int* __restrict__ offsets, int* __restrict__ expert_ids, int* __restrict__ num_post_padded,
+                                int* __restrict__ sorted_ids) {
+  __shared__ int total;
+  if (threadIdx.x == 0) {
+    int off = 0;
+    for (int e = 0; e < num_experts; ++e) {
+      offsets[e] = off;
+      const int nblk = (counts[e] + block - 1) / block;
+      for (int b = 0; b < nblk; ++b) expert_ids[off / block + b] = e;
+      off += nblk * block;
+    }
+    total = off;
+    *num_post_padded = off;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < capacity; i += blockDim.x) sorted_ids[i] = numel;
+  (void)total;
+}
+// One warp per expert: stable compaction (ascending flat id) of its entries.
+__global__ void moe_scatter_kernel(const int* __restrict__ topk_ids, int numel, int num_experts,
+                                   const int* __restrict__ offsets, int* __restrict__ sorted_ids) {
+  const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (e >= num_experts) return;
+  int pos = offsets[e];
+  for (int base = 0; base < numel; base += 32) {
+    const int i = base + lane;
+    const bool hit = i < numel && topk_ids[i] == e;
+    const unsigned mask = __ballot_sync(0xffffffffu, hit);
+    if (hit) sorted_ids[pos + __popc(mask & ((1u << lane) - 1u))] = i;
+    pos += __popc(mask);
+  }
+}
+
 }  // namespace hm

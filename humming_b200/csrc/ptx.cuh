@@ -131,6 +131,16 @@ HM_DEVICE uint64_t l2_policy_evict_last() {
   return p;
 }
 
+// 16-byte asynchronous copy global -> shared; src_bytes = 0 writes zeros.
+HM_DEVICE void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+HM_DEVICE void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+HM_DEVICE void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
 // 2-D tiled TMA load global -> shared.  x (innermost coordinate) times the
 // element size must be a multiple of 16 bytes.
 HM_DEVICE void tma_load_2d(uint32_t dst, const CUtensorMap* tmap, int x, int y, uint32_t bar) {

@@ -310,11 +310,26 @@ class HummingMethod(torch.nn.Module):
         ``activation_type``, ``use_stream_k`` ...).  The reference compiles six
         M-bucket kernels here (``humming/layer.py:403-451``); this library plans
         tile size and K split natively per call, so no buckets are installed."""
+        meta = layer.humming_metas[sublayer_name]
         opts = layer.humming_kernel_options[sublayer_name]
         opts.update(kwargs)
         act = opts.get("activation_type")
         if act not in (None, "none"):
             raise NotImplementedError(f"humming_b200: fused activation {act!r} is not built")
+        if meta.num_experts is not None and opts.get("is_moe", True):
+            top_k = opts.get("top_k", 0)
+            if top_k:
+                # Token tile (= the block size sorted_token_ids must be aligned to) by
+                # token count, so that a tile roughly matches the rows one expert gets:
+                # [min_m, max_m, block] triples as in the reference's
+                # humming_block_size_configs (humming/layer.py:493-499).
+                table, lo = [], 0
+                for block in (16, 32, 64):
+                    hi = max(lo, block * meta.num_experts // top_k)
+                    table += [lo, hi, block]
+                    lo = hi + 1
+                table += [lo, 1 << 31, 128]
+                layer.humming_block_size_configs[sublayer_name] = table
 
     @classmethod
     def add_kernel_config(cls, layer, min_shape_m: int, max_shape_m: int, block_shape, warp_shape=None,
@@ -356,8 +371,11 @@ class HummingMethod(torch.nn.Module):
         meta: HummingLayerMeta = layer.humming_metas[sublayer_name]
         if not layer.humming_prepared[sublayer_name]:
             raise RuntimeError("call finish_load before forward")
-        if meta.num_experts is not None or sorted_token_ids is not None:
-            raise NotImplementedError("humming_b200: the MoE (indexed) GEMM is not built yet")
+        if meta.num_experts is not None:
+            return cls._forward_moe(layer, meta, inputs, outputs, topk_weights, sorted_token_ids, expert_ids,
+                                    num_tokens_post_padded, sublayer_name)
+        if sorted_token_ids is not None:
+            raise ValueError("routing tensors given to a dense layer")
         inputs, input_scale = cls.may_quant_input(meta, inputs, input_scale)
         a = inputs.reshape(-1, inputs.size(-1))
         if a.stride(-1) != 1 or (a.stride(0) * a.element_size()) % 16 or a.data_ptr() % 16:
@@ -391,6 +409,61 @@ class HummingMethod(torch.nn.Module):
         runtime.gemm(desc, a, getattr(layer, meta.weight_name), getattr(layer, meta.weight_scale_name, None),
                      getattr(layer, meta.zero_point_name, None), getattr(layer, meta.bias_name, None),
                      outputs.view(-1, meta.shape_n), ws, a_scale=input_scale)
+        return outputs
+
+    @classmethod
+    def moe_block_size(cls, layer, num_tokens: int, sublayer_name: str = "") -> int:
+        """Block size ``sorted_token_ids`` must be aligned to for ``num_tokens`` tokens
+        (needs ``prepare_default_kernel_configs(layer, is_moe=True, top_k=...)``)."""
+        cfg = layer.humming_block_size_configs[sublayer_name]
+        for i in range(0, len(cfg), 3):
+            if cfg[i] <= num_tokens <= cfg[i + 1]:
+                return cfg[i + 2]
+        raise RuntimeError("no MoE block-size table: call prepare_default_kernel_configs(layer, is_moe=True, top_k=...)")
+
+    @classmethod
+    def _forward_moe(cls, layer, meta, inputs, outputs, topk_weights, sorted_token_ids, expert_ids,
+                     num_tokens_post_padded, sublayer_name):
+        """Indexed GEMM over the experts (reference docs/CONFIG.md "MoE Config"):
+        up projection reads row ``id // top_k`` of ``inputs (M, K)``, down projection row
+        ``id`` of ``inputs (M, top_k, K)`` and multiplies by ``topk_weights``; both write
+        row ``id`` of ``outputs (M, top_k, N)``."""
+        opts = layer.humming_kernel_options[sublayer_name]
+        top_k = opts.get("top_k", 0)
+        is_down = bool(opts.get("is_moe_down", False))
+        if not top_k:
+            raise RuntimeError("MoE forward needs prepare_default_kernel_configs(layer, is_moe=True, top_k=...)")
+        if sorted_token_ids is None or expert_ids is None or num_tokens_post_padded is None:
+            raise ValueError("MoE forward needs sorted_token_ids, expert_ids and num_tokens_post_padded")
+        if is_down and topk_weights is None:
+            raise ValueError("the down projection needs topk_weights")
+        num_tokens = inputs.size(0)
+        a = inputs.reshape(-1, inputs.size(-1))
+        if a.stride(-1) != 1 or (a.stride(0) * a.element_size()) % 16 or a.data_ptr() % 16:
+            a = a.contiguous()
+        if a.size(1) != meta.shape_k or a.size(0) != num_tokens * (top_k if is_down else 1):
+            raise ValueError(f"inputs of shape {tuple(inputs.shape)} do not fit a "
+                             f"{'down' if is_down else 'up'} projection with K={meta.shape_k}, top_k={top_k}")
+        if a.dtype != dtypes.torch_dtype_map[meta.a_dtype]:
+            raise ValueError(f"inputs are {a.dtype}, layer expects {meta.a_dtype}")
+        block = cls.moe_block_size(layer, num_tokens, sublayer_name)
+        if sorted_token_ids.numel() % block:
+            raise ValueError(f"sorted_token_ids must be aligned to blocks of {block} for {num_tokens} tokens")
+        c_dtype = dtypes.torch_dtype_map[meta.c_dtype]
+        if outputs is None:
+            outputs = torch.empty((num_tokens, top_k, meta.shape_n), dtype=c_dtype, device=a.device)
+        else:
+            assert outputs.dtype == c_dtype and outputs.is_contiguous() and outputs.numel() == num_tokens * top_k * meta.shape_n
+        if num_tokens == 0:
+            return outputs
+        desc = cls._desc(meta, m_tile=block, top_k=top_k, is_moe_down=is_down)
+        ws = cls._workspace(layer, runtime.moe_workspace_bytes(desc, sorted_token_ids.numel()), a.device)
+        ids = sorted_token_ids if sorted_token_ids.dtype == torch.int32 else sorted_token_ids.int()
+        tkw = None if topk_weights is None else topk_weights.reshape(-1).float().contiguous()
+        runtime.moe_gemm(desc, num_tokens * top_k, a, getattr(layer, meta.weight_name),
+                         getattr(layer, meta.weight_scale_name, None), getattr(layer, meta.zero_point_name, None),
+                         getattr(layer, meta.bias_name, None), tkw, ids.contiguous(), expert_ids.int().contiguous(),
+                         num_tokens_post_padded.reshape(-1).int(), outputs.view(-1, meta.shape_n), ws)
         return outputs
 
     @classmethod

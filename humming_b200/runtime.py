@@ -149,6 +149,45 @@ def gemm(desc: native.GemmDesc, a: torch.Tensor, w, w_scale, w_zp, bias, c: torc
     return c
 
 
+def moe_align_block_size(topk_ids: torch.Tensor, num_experts: int, block: int):
+    """-> (sorted_token_ids, expert_ids, num_tokens_post_padded), all int32 on the device.
+
+    sorted_token_ids has a fixed capacity (numel + experts * (block - 1), rounded up
+    to the block); entries past num_tokens_post_padded hold the sentinel."""
+    _require_cuda(topk_ids)
+    ids = topk_ids.reshape(-1).to(torch.int32).contiguous()
+    numel = ids.numel()
+    capacity = (numel + num_experts * (block - 1) + block - 1) // block * block
+    dev = ids.device
+    sorted_ids = torch.empty(capacity, dtype=torch.int32, device=dev)
+    expert_ids = torch.empty(capacity // block, dtype=torch.int32, device=dev)
+    total = torch.empty(1, dtype=torch.int32, device=dev)
+    scratch = torch.empty(2 * num_experts, dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        native.check(native.lib.hm_moe_align_block_size(_ptr(ids), numel, num_experts, block, _ptr(sorted_ids), capacity,
+                                                        _ptr(expert_ids), _ptr(total), _ptr(scratch), _stream(dev)))
+    return sorted_ids, expert_ids, total
+
+
+def moe_workspace_bytes(desc: native.GemmDesc, capacity: int) -> int:
+    n = native.lib.hm_moe_gemm_workspace_bytes(ctypes.byref(desc), capacity)
+    if n == 0:
+        raise ValueError(native.last_error())
+    return n
+
+
+def moe_gemm(desc: native.GemmDesc, num_valid: int, a, w, w_scale, w_zp, bias, topk_weights, sorted_ids, expert_ids,
+             num_post_padded, c, workspace):
+    """Enqueue one indexed (MoE) GEMM on the current stream of ``a``'s device."""
+    _require_cuda(a, w, w_scale, w_zp, bias, topk_weights, sorted_ids, expert_ids, num_post_padded, c, workspace)
+    with torch.cuda.device(a.device):
+        native.check(native.lib.hm_moe_gemm(
+            ctypes.byref(desc), num_valid, _ptr(a), a.stride(0), _ptr(w), _ptr(w_scale), _ptr(w_zp), _ptr(bias),
+            _ptr(topk_weights), _ptr(sorted_ids), sorted_ids.numel(), _ptr(expert_ids), _ptr(num_post_padded), _ptr(c),
+            c.stride(0), _ptr(workspace), workspace.nelement() * workspace.element_size(), _stream(a.device)))
+    return c
+
+
 def check_status(workspace: torch.Tensor):
     """Synchronise and raise if a kernel using ``workspace`` aborted."""
     with torch.cuda.device(workspace.device):

@@ -159,6 +159,38 @@ HM_API int hm_gemm(const hm_gemm_desc* desc, int64_t m, const void* a, int64_t l
                    const void* w, const void* w_scale, const void* w_zp, const void* bias, void* c, int64_t ldc,
                    void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- MoE (indexed GEMM) ------------------------------------------------------ */
+
+/* Groups the flat (token, slot) entries of topk_ids[numel] (expert id each) by
+ * expert, ascending id inside an expert, each expert padded to a multiple of
+ * `block` with the sentinel `numel`: sorted_ids[capacity] (capacity >=
+ * numel + num_experts * (block - 1), rounded up to a multiple of block),
+ * expert_ids[capacity / block], num_post_padded[1].  scratch: 2 * num_experts
+ * ints.  The reference leaves this to the caller and does it in a Python loop
+ * (humming/utils/test.py:154-183, "TODO: moe_align_block_size cuda kernel"). */
+HM_API int hm_moe_align_block_size(const int32_t* topk_ids, int64_t numel, int num_experts, int block,
+                                   int32_t* sorted_ids, int64_t capacity, int32_t* expert_ids,
+                                   int32_t* num_post_padded, int32_t* scratch, void* stream);
+
+/* Workspace bytes of hm_moe_gemm for a sorted_ids buffer of `capacity` entries
+ * (desc->m_tile = block size used for the alignment: 16, 32, 64 or 128). */
+HM_API size_t hm_moe_gemm_workspace_bytes(const hm_gemm_desc* desc, int64_t capacity);
+
+/* Indexed GEMM over all experts (desc->num_experts > 0, desc->top_k,
+ * desc->is_moe_down, desc->m_tile = alignment block).  Up projection
+ * (is_moe_down = 0): a is (tokens, K), row id / top_k is read; down projection:
+ * a is (tokens * top_k, K), row id is read and the result is multiplied by
+ * topk_weights[id] (fp32).  Row id of c (tokens * top_k, shape_n) is written for
+ * every id < num_valid = tokens * top_k; padding entries are skipped.
+ * w / w_scale / w_zp: prepared buffers with a leading expert dimension.
+ * Replaces launch_humming with is_moe (humming/csrc/launcher/launcher.cpp:61-161,
+ * humming/include/humming/scheduler.cuh:158-182, docs/CONFIG.md "MoE Config"). */
+HM_API int hm_moe_gemm(const hm_gemm_desc* desc, int64_t num_valid, const void* a, int64_t lda, const void* w,
+                       const void* w_scale, const void* w_zp, const void* bias, const float* topk_weights,
+                       const int32_t* sorted_ids, int64_t capacity, const int32_t* expert_ids,
+                       const int32_t* num_post_padded, void* c, int64_t ldc, void* workspace, size_t workspace_bytes,
+                       void* stream);
+
 /* Same computation as hm_gemm for callers that cannot provide a workspace.
  * No counterpart in the reference implementation.
  *

@@ -200,6 +200,68 @@ def run_point(args):
                       "algorithmic_bytes": gemm_bytes(m, n, k), "flops": gemm_flops(m, n, k)}), flush=True)
 
 
+def run_moe(args, rank, world, local_rank):
+    """`--workload moe`: BASELINE.json configs[3], a Qwen3-30B-A3B-shaped MoE layer (128 experts, top-8,
+    hidden 2048, expert intermediate 768, uint4 symmetric weights, bf16 group-128 scales), expert-parallel
+    over the ranks (128 / world experts per GPU, tokens split evenly), NCCL all-to-all dispatch/combine.
+    Reports tokens/s for `--tokens` tokens in total (strong scaling)."""
+    import torch.distributed as dist
+    from humming_b200.moe import HummingMoE
+
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    experts, top_k, hidden, inter = 128, 8, 2048, 768
+    moe = HummingMoE(hidden, inter, experts, top_k).to(dev)
+    for local, e in enumerate(moe.ep.owned_experts()):
+        gen = torch.Generator(device=dev).manual_seed(1000 + e)
+        gu = torch.randint(0, 16, (2 * inter, hidden), generator=gen, dtype=torch.int32, device=dev)
+        gus = (torch.randn((2 * inter, hidden // GROUP), generator=gen, device=dev).abs() * 0.02 + 1e-3).bfloat16()
+        dn = torch.randint(0, 16, (hidden, inter), generator=gen, dtype=torch.int32, device=dev)
+        dns = (torch.randn((hidden, inter // GROUP), generator=gen, device=dev).abs() * 0.02 + 1e-3).bfloat16()
+        moe.load_expert(local, gu, gus, dn, dns)
+    moe.finish_load()
+    results = []
+    for total_tokens in [int(t) for t in args.tokens.split(",")]:
+        tokens = total_tokens // world + (1 if rank < total_tokens % world else 0)
+        gen = torch.Generator(device=dev).manual_seed(7 + rank)
+        x = torch.randn((tokens, hidden), generator=gen, device=dev).bfloat16()
+        logits = torch.randn((tokens, experts), generator=gen, device=dev)
+        for _ in range(max(args.warmup, 3)):
+            moe(x, logits)
+        moe.check_status()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            moe(x, logits)
+        e1.record()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / args.steps], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        results.append({"tokens": total_tokens, "ms_per_step": float(t), "tokens_per_s": total_tokens / (float(t) * 1e-3)})
+    if rank != 0:
+        return
+    top = results[-1]
+    flops_per_token = 2.0 * top_k * (2 * inter * hidden + hidden * inter)
+    line = {
+        "metric": "MoE layer throughput, Qwen3-30B-A3B-shaped (128 experts, top-8, W4A16 bf16)", "value": top["tokens_per_s"],
+        "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": top["ms_per_step"],
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "qwen3-30b-a3b MoE layer: route, align, up GEMM, silu*mul, down GEMM, top-k sum",
+                   "experts": experts, "top_k": top_k, "hidden": hidden, "intermediate": inter, "tokens_total": top["tokens"],
+                   "parallelism": f"ep{world}" if world > 1 else "single GPU",
+                   "timing": "eager, CUDA events, max over ranks (the exchange sizes are read on the host)"},
+        "tflops": top["tokens_per_s"] * flops_per_token / 1e12,
+        "sweep": results,
+    }
+    print(json.dumps(line), flush=True)
+
+
 def run_ours(args, rank, world, local_rank):
     import torch.distributed as dist
     from humming_b200 import runtime
@@ -374,6 +436,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="dense", choices=["dense", "moe"])
+    ap.add_argument("--tokens", default="32,512,4096", help="moe workload: total token counts to time, the last one is the headline")
     ap.add_argument("--point", default=None, help="PROJ:M, e.g. gate_up:16 -- launch only this sweep point a few times")
     args = ap.parse_args()
 
@@ -391,7 +455,10 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     try:
-        run_ours(args, rank, world, local_rank)
+        if args.workload == "moe":
+            run_moe(args, rank, world, local_rank)
+        else:
+            run_ours(args, rank, world, local_rank)
     finally:
         if world > 1:
             import torch.distributed as dist

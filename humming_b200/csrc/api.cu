@@ -12,6 +12,7 @@
 #include <mutex>
 
 #include "gemm_w4a16.cuh"
+#include "moe_ops.cuh"
 #include "prep.cuh"
 #include "sched.cuh"
 
@@ -589,6 +590,44 @@ int hm_moe_gemm(const hm_gemm_desc* desc, int64_t num_valid, const void* a, int6
     case 128: return dispatch_moe<128>(bf16, desc->has_zp != 0, p, sms, s);
   }
   return fail(HM_ERR_INVALID, "no MoE kernel for token tile %d", mt);
+}
+
+int hm_moe_route(const float* logits, int64_t tokens, int experts, int top_k, int use_softmax, int renormalize,
+                 int32_t* topk_ids, float* topk_weights, void* stream) {
+  if (logits == nullptr || topk_ids == nullptr || topk_weights == nullptr) return fail(HM_ERR_INVALID, "NULL pointer");
+  if (tokens < 0 || experts <= 0 || experts > 1024 || top_k <= 0 || top_k > 32 || top_k > experts)
+    return fail(HM_ERR_INVALID, "routing needs 1 <= top_k <= min(32, experts) and experts <= 1024");
+  if (tokens == 0) return HM_OK;
+  hm::moe_route_kernel<<<blocks_for(tokens * 32, 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      logits, static_cast<int>(tokens), experts, top_k, use_softmax, renormalize, topk_ids, topk_weights);
+  HM_CUDA_OK(cudaGetLastError());
+  return HM_OK;
+}
+
+int hm_silu_mul(const void* x, void* out, int64_t rows, int inter, int dtype, void* stream) {
+  if (x == nullptr || out == nullptr) return fail(HM_ERR_INVALID, "NULL pointer");
+  if (rows < 0 || inter <= 0) return fail(HM_ERR_INVALID, "bad rows / inter");
+  if (rows == 0) return HM_OK;
+  auto s = static_cast<cudaStream_t>(stream);
+  const unsigned blocks = blocks_for(rows * inter, 256);
+  if (dtype == HM_BF16) hm::silu_mul_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(out), rows, inter);
+  else if (dtype == HM_F16) hm::silu_mul_kernel<__half><<<blocks, 256, 0, s>>>(static_cast<const __half*>(x), static_cast<__half*>(out), rows, inter);
+  else return fail(HM_ERR_INVALID, "dtype code %d not accepted", dtype);
+  HM_CUDA_OK(cudaGetLastError());
+  return HM_OK;
+}
+
+int hm_topk_sum(const void* x, void* out, int64_t tokens, int top_k, int width, int dtype, void* stream) {
+  if (x == nullptr || out == nullptr) return fail(HM_ERR_INVALID, "NULL pointer");
+  if (tokens < 0 || top_k <= 0 || width <= 0) return fail(HM_ERR_INVALID, "bad tokens / top_k / width");
+  if (tokens == 0) return HM_OK;
+  auto s = static_cast<cudaStream_t>(stream);
+  const unsigned blocks = blocks_for(tokens * width, 256);
+  if (dtype == HM_BF16) hm::topk_sum_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(out), tokens, top_k, width);
+  else if (dtype == HM_F16) hm::topk_sum_kernel<__half><<<blocks, 256, 0, s>>>(static_cast<const __half*>(x), static_cast<__half*>(out), tokens, top_k, width);
+  else return fail(HM_ERR_INVALID, "dtype code %d not accepted", dtype);
+  HM_CUDA_OK(cudaGetLastError());
+  return HM_OK;
 }
 
 // ---- hm_gemm_static_scratch ------------------------------------------------------

@@ -1,0 +1,145 @@
+"""A quantized MoE layer on top of the two indexed GEMMs, single GPU or
+expert-parallel over ``torch.distributed``.
+
+The reference stops at the two GEMMs (routing, block alignment, SiLU*mul and
+the sum over top-k are left to its caller, and it is single-GPU only).  The
+benchmark configurations time a whole MoE layer, so this module fixes one:
+
+    route (softmax -> top-k -> renormalise)  ->  [dispatch]  ->  align  ->
+    up GEMM (gate|up)  ->  silu(gate) * up  ->  down GEMM x routing weight  ->
+    [combine]  ->  sum over top-k
+
+Expert parallelism: rank r owns experts [r*E/W, (r+1)*E/W); every rank routes
+its own tokens, sends one activation row per (token, slot) entry to the rank
+that owns the entry's expert (``all_to_all_single``: rows, local expert ids,
+routing weights), runs the indexed GEMMs over the rows it received (each row is
+its own "token" with top_k = 1), and sends the weighted expert outputs back; the
+source rank un-permutes and sums over top-k.  The exchange is data-dependent,
+so the split sizes travel first (one small all-to-all and a host read).
+"""
+from typing import Callable, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+class ExpertParallel:
+    """Dispatch / combine plumbing, independent of how the experts are computed
+    (device-agnostic: the CPU tests drive it over gloo with a reference expert
+    function)."""
+
+    def __init__(self, num_experts: int, group: Optional["dist.ProcessGroup"] = None):
+        self.group = group
+        self.world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
+        self.rank = dist.get_rank(group) if self.world > 1 else 0
+        if num_experts % self.world:
+            raise ValueError(f"{num_experts} experts do not divide over {self.world} ranks")
+        self.num_experts = num_experts
+        self.experts_per_rank = num_experts // self.world
+
+    def owned_experts(self) -> range:
+        return range(self.rank * self.experts_per_rank, (self.rank + 1) * self.experts_per_rank)
+
+    def _exchange_counts(self, send_counts: torch.Tensor) -> Tuple[List[int], List[int]]:
+        recv_counts = torch.empty_like(send_counts)
+        dist.all_to_all_single(recv_counts, send_counts, group=self.group)
+        return send_counts.tolist(), recv_counts.tolist()
+
+    def _all_to_all(self, x: torch.Tensor, out_splits: List[int], in_splits: List[int]) -> torch.Tensor:
+        out = x.new_empty((sum(out_splits),) + tuple(x.shape[1:]))
+        dist.all_to_all_single(out, x.contiguous(), output_split_sizes=out_splits, input_split_sizes=in_splits, group=self.group)
+        return out
+
+    def forward(self, hidden: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor,
+                experts_fn: Callable[[torch.Tensor, torch.Tensor, torch.Tensor], torch.Tensor]) -> torch.Tensor:
+        """hidden (T, H); topk_ids / topk_weights (T, k).  ``experts_fn(rows, local_expert_ids, weights)``
+        returns the weighted expert output of every row.  Returns (T, k, H): per-slot outputs, to be
+        summed over k by the caller."""
+        tokens, k = topk_ids.shape
+        flat_e = topk_ids.reshape(-1).long()
+        flat_w = topk_weights.reshape(-1).float()
+        if self.world == 1:
+            rows = hidden.index_select(0, torch.arange(tokens * k, device=hidden.device) // k)
+            out = experts_fn(rows, flat_e.int(), flat_w)
+            return out.view(tokens, k, -1)
+        dest = flat_e // self.experts_per_rank
+        order = torch.argsort(dest, stable=True)
+        send_counts = torch.bincount(dest, minlength=self.world)
+        in_splits, out_splits = self._exchange_counts(send_counts)
+        rows = hidden.index_select(0, order // k)
+        local_e = (flat_e.index_select(0, order) % self.experts_per_rank).int()
+        w = flat_w.index_select(0, order)
+        recv_rows = self._all_to_all(rows, out_splits, in_splits)
+        recv_e = self._all_to_all(local_e, out_splits, in_splits)
+        recv_w = self._all_to_all(w, out_splits, in_splits)
+        out_rows = experts_fn(recv_rows, recv_e, recv_w)
+        back = self._all_to_all(out_rows, in_splits, out_splits)
+        result = back.new_empty((tokens * k, back.size(-1)))
+        result.index_copy_(0, order, back)
+        return result.view(tokens, k, -1)
+
+
+class HummingMoE(torch.nn.Module):
+    """Quantized MoE layer (uint4 / int4 weights, 16-bit activations) built from
+    two MoE ``HummingLayer``s holding this rank's experts."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, num_experts: int, top_k: int, dtype: str = "bfloat16",
+                 b_dtype: str = "uint4", weight_scale_group_size: int = 128, has_dynamic_zp: bool = False,
+                 group: Optional["dist.ProcessGroup"] = None):
+        super().__init__()
+        from humming_b200.layer import HummingLayer
+
+        self.ep = ExpertParallel(num_experts, group)
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.num_experts, self.top_k = num_experts, top_k
+        common = dict(a_dtype=dtype, b_dtype=b_dtype, c_dtype=dtype, bs_dtype=dtype, weight_scale_group_size=weight_scale_group_size,
+                      has_dynamic_zp=has_dynamic_zp, num_experts=self.ep.experts_per_rank)
+        self.up = HummingLayer(shape_n=2 * intermediate_size, shape_k=hidden_size, **common)    # rows [gate | up]
+        self.down = HummingLayer(shape_n=hidden_size, shape_k=intermediate_size, **common)
+
+    def load_expert(self, local_expert: int, gate_up: torch.Tensor, gate_up_scale: torch.Tensor, down: torch.Tensor,
+                    down_scale: torch.Tensor, gate_up_zp=None, down_zp=None):
+        """Codes (N, K) int32 and scales (N, K/g) of one locally owned expert."""
+        self.up.load_weight(weight=gate_up, weight_scale=gate_up_scale, zero_point=gate_up_zp, expert_id=local_expert)
+        self.down.load_weight(weight=down, weight_scale=down_scale, zero_point=down_zp, expert_id=local_expert)
+
+    def finish_load(self):
+        from humming_b200.layer import HummingMethod
+
+        # Rows reaching the experts through dispatch are one "token" each (top_k = 1);
+        # on a single GPU the GEMMs index the un-duplicated hidden states directly.
+        k = self.top_k if self.ep.world == 1 else 1
+        for layer, down in ((self.up, False), (self.down, True)):
+            HummingMethod.finish_load(layer)
+            HummingMethod.prepare_default_kernel_configs(layer, is_moe=True, top_k=k, is_moe_down=down)
+
+    def _experts(self, rows: torch.Tensor, local_e: torch.Tensor, w: torch.Tensor, top_k: int) -> torch.Tensor:
+        """rows (T, H) with T*top_k routed entries (local_e, w flat) -> weighted outputs (T*top_k, H)."""
+        from humming_b200 import runtime
+        from humming_b200.layer import HummingMethod
+
+        tokens = rows.size(0)
+        if tokens == 0:
+            return rows.new_empty((0, self.hidden_size))
+        block = HummingMethod.moe_block_size(self.up, tokens)
+        sorted_ids, expert_ids, total = runtime.moe_align_block_size(local_e, self.ep.experts_per_rank, block)
+        routing = dict(sorted_token_ids=sorted_ids, expert_ids=expert_ids, num_tokens_post_padded=total)
+        h = self.up(inputs=rows, **routing)                                   # (T, k, 2I)
+        act = runtime.silu_mul(h.view(tokens * top_k, 2 * self.intermediate_size))
+        out = self.down(inputs=act.view(tokens, top_k, self.intermediate_size), topk_weights=w, **routing)
+        return out.view(tokens * top_k, self.hidden_size)
+
+    def forward(self, hidden_states: torch.Tensor, router_logits: torch.Tensor) -> torch.Tensor:
+        from humming_b200 import runtime
+
+        topk_ids, topk_w = runtime.moe_route(router_logits, self.top_k, use_softmax=True, renormalize=True)
+        if self.ep.world == 1:
+            per_slot = self._experts(hidden_states, topk_ids.view(-1), topk_w.view(-1), self.top_k)
+            per_slot = per_slot.view(hidden_states.size(0), self.top_k, self.hidden_size)
+        else:
+            per_slot = self.ep.forward(hidden_states, topk_ids, topk_w, lambda r, e, w: self._experts(r, e, w, 1))
+        return runtime.topk_sum(per_slot.contiguous())
+
+    def check_status(self):
+        self.up.check_status()
+        self.down.check_status()

@@ -188,6 +188,43 @@ def moe_gemm(desc: native.GemmDesc, num_valid: int, a, w, w_scale, w_zp, bias, t
     return c
 
 
+def moe_route(logits: torch.Tensor, top_k: int, use_softmax: bool = True, renormalize: bool = True):
+    """fp32 logits (tokens, experts) -> (topk_ids int32 (tokens, k), topk_weights fp32 (tokens, k))."""
+    _require_cuda(logits)
+    x = logits.float().contiguous()
+    tokens, experts = x.shape
+    ids = torch.empty((tokens, top_k), dtype=torch.int32, device=x.device)
+    wts = torch.empty((tokens, top_k), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        native.check(native.lib.hm_moe_route(_ptr(x), tokens, experts, top_k, int(use_softmax), int(renormalize), _ptr(ids),
+                                             _ptr(wts), _stream(x.device)))
+    return ids, wts
+
+
+def silu_mul(x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x (rows, 2*inter) = [gate | up] -> silu(gate) * up, (rows, inter)."""
+    _require_cuda(x)
+    assert x.is_contiguous() and x.dtype in _TORCH_TO_NATIVE
+    rows, two = x.shape
+    if out is None:
+        out = torch.empty((rows, two // 2), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        native.check(native.lib.hm_silu_mul(_ptr(x), _ptr(out), rows, two // 2, _TORCH_TO_NATIVE[x.dtype], _stream(x.device)))
+    return out
+
+
+def topk_sum(x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x (tokens, top_k, width) -> sum over top_k, (tokens, width)."""
+    _require_cuda(x)
+    assert x.is_contiguous() and x.dtype in _TORCH_TO_NATIVE
+    tokens, top_k, width = x.shape
+    if out is None:
+        out = torch.empty((tokens, width), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        native.check(native.lib.hm_topk_sum(_ptr(x), _ptr(out), tokens, top_k, width, _TORCH_TO_NATIVE[x.dtype], _stream(x.device)))
+    return out
+
+
 def check_status(workspace: torch.Tensor):
     """Synchronise and raise if a kernel using ``workspace`` aborted."""
     with torch.cuda.device(workspace.device):

@@ -191,6 +191,24 @@ HM_API int hm_moe_gemm(const hm_gemm_desc* desc, int64_t num_valid, const void* 
                        const int32_t* num_post_padded, void* c, int64_t ldc, void* workspace, size_t workspace_bytes,
                        void* stream);
 
+/* Routing: per token, optional softmax over logits[tokens, experts] (fp32), the
+ * top_k largest (ties to the lowest expert id), optionally renormalised to sum 1.
+ * Not part of the reference (its tests draw top-k of random logits on the host,
+ * humming/utils/test.py:154-157); needed for the MoE layer the benchmark times. */
+HM_API int hm_moe_route(const float* logits, int64_t tokens, int experts, int top_k, int use_softmax, int renormalize,
+                        int32_t* topk_ids, float* topk_weights, void* stream);
+
+/* out[r, j] = silu(x[r, j]) * x[r, inter + j] for x = [gate | up] of width
+ * 2 * inter, dtype HM_F16 / HM_BF16.  The unfused form of the reference's
+ * silu_glu epilogue (humming/include/humming/arith/activation.cuh, docs/CONFIG.md
+ * "Epilogue Config"). */
+HM_API int hm_silu_mul(const void* x, void* out, int64_t rows, int inter, int dtype, void* stream);
+
+/* out[t, j] = sum over k of x[t, k, j] (fp32 accumulation), dtype HM_F16 / HM_BF16:
+ * the reduction over top_k that follows the down projection (the reference
+ * leaves (M, top_k, N) unreduced, humming/csrc/launcher/tensor.h:104-110). */
+HM_API int hm_topk_sum(const void* x, void* out, int64_t tokens, int top_k, int width, int dtype, void* stream);
+
 /* Same computation as hm_gemm for callers that cannot provide a workspace.
  * No counterpart in the reference implementation.
  *

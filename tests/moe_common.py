@@ -1,0 +1,35 @@
+"""Shared pieces of the MoE layer tests: seeded expert weights and the CPU reference."""
+import torch
+
+
+def make_expert_weights(num_experts, hidden, inter, seed=0):
+    gen = torch.Generator(device="cpu").manual_seed(seed)
+    up_codes = torch.randint(0, 16, (num_experts, 2 * inter, hidden), generator=gen, dtype=torch.int32)
+    up_scales = (torch.randn((num_experts, 2 * inter, hidden // 128), generator=gen).abs() * 0.02 + 1e-3).bfloat16()
+    down_codes = torch.randint(0, 16, (num_experts, hidden, inter), generator=gen, dtype=torch.int32)
+    down_scales = (torch.randn((num_experts, hidden, inter // 128), generator=gen).abs() * 0.02 + 1e-3).bfloat16()
+    return up_codes, up_scales, down_codes, down_scales
+
+
+def dequant(codes, scales):
+    """fp32 (q - 8) * s, rounded once to bf16 (what the kernels multiply by)."""
+    return ((codes.float() - 8.0) * scales.float().repeat_interleave(128, -1)).bfloat16().float()
+
+
+def moe_layer_reference(hidden_states, router_logits, weights, top_k):
+    """route -> per-expert gate|up -> silu*up -> down x weight -> sum, with the
+    pipeline's bf16 roundings (GEMM outputs, activation, per-slot outputs, sum)."""
+    up_codes, up_scales, down_codes, down_scales = weights
+    inter = down_codes.size(-1)
+    probs = torch.softmax(router_logits.float(), -1)
+    w, ids = probs.topk(top_k, 1)
+    w = w / w.sum(-1, keepdim=True)
+    x = hidden_states.float()
+    out = torch.zeros((x.size(0), top_k, x.size(1)))
+    for e in ids.unique().tolist():
+        wu, wd = dequant(up_codes[e], up_scales[e]), dequant(down_codes[e], down_scales[e])
+        tok, slot = torch.where(ids == e)
+        h = (x[tok] @ wu.T).bfloat16().float()
+        act = (torch.nn.functional.silu(h[:, :inter]) * h[:, inter:]).bfloat16().float()
+        out[tok, slot] = ((act @ wd.T) * w[tok, slot, None]).bfloat16().float()
+    return out.sum(1).bfloat16(), ids, w

@@ -1,0 +1,52 @@
+"""Expert-parallel MoE layer on two GPUs over NCCL against the single-process
+CPU reference.  Skipped where fewer than two GPUs are visible."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from moe_common import make_expert_weights, moe_layer_reference
+
+pytestmark = pytest.mark.gpu
+
+EXPERTS, TOP_K, HIDDEN, INTER, TOKENS = 16, 4, 512, 256, 40
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, outdir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from humming_b200.moe import HummingMoE
+
+        dev = torch.device("cuda", rank)
+        weights = make_expert_weights(EXPERTS, HIDDEN, INTER, seed=3)
+        moe = HummingMoE(HIDDEN, INTER, EXPERTS, TOP_K).to(dev)
+        for local, e in enumerate(moe.ep.owned_experts()):
+            moe.load_expert(local, weights[0][e].to(dev), weights[1][e].to(dev), weights[2][e].to(dev), weights[3][e].to(dev))
+        moe.finish_load()
+        gen = torch.Generator(device="cpu").manual_seed(100 + rank)
+        x = torch.randn((TOKENS + 7 * rank, HIDDEN), generator=gen).bfloat16()
+        logits = torch.randn((TOKENS + 7 * rank, EXPERTS), generator=gen)
+        out = moe(x.to(dev), logits.to(dev))
+        moe.check_status()
+        ref, _, _ = moe_layer_reference(x, logits, weights, TOP_K)
+        torch.testing.assert_close(out.float().cpu(), ref.float(), rtol=0.05, atol=0.1)
+        open(os.path.join(outdir, f"ok{rank}"), "w").close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_expert_parallel_moe_two_gpus(tmp_path):
+    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    assert sorted(os.listdir(tmp_path)) == ["ok0", "ok1"]

@@ -73,15 +73,22 @@ int validate_desc(const hm_gemm_desc* d) {
   if (d->group_size < 0) return fail(HM_ERR_INVALID, "group_size must be >= 0");
   const int g = d->group_size == 0 ? d->shape_k : d->group_size;
   if (d->shape_k % g != 0) return fail(HM_ERR_INVALID, "shape_k=%d not divisible by group_size=%d", d->shape_k, g);
-  if (is16(d->a_dtype)) {
-    if (d->b_dtype != HM_UINT(4) && d->b_dtype != HM_INT(4))
-      return fail(HM_ERR_UNSUPPORTED, "16-bit activations: weight dtype code 0x%x not built (uint4/int4 only)", d->b_dtype);
+  // Activations: 16-bit, or e4m3 with one fp32 scale per token (converted exactly
+  // to the 16-bit compute type = c_dtype before the GEMM, the scale applied in
+  // the epilogue).  Weights: 4-bit integers with 16-bit group scales, or MXFP4.
+  if (!is16(d->a_dtype) && d->a_dtype != HM_E4M3) return fail(HM_ERR_UNSUPPORTED, "a_dtype code %d not built", d->a_dtype);
+  if (!is16(d->c_dtype)) return fail(HM_ERR_UNSUPPORTED, "c_dtype must be float16 or bfloat16");
+  if (is16(d->a_dtype) && d->c_dtype != d->a_dtype) return fail(HM_ERR_UNSUPPORTED, "c_dtype must equal a 16-bit a_dtype");
+  if (d->b_dtype == HM_E2M1) {
+    if (d->bs_dtype != HM_E8M0 || g != 32) return fail(HM_ERR_UNSUPPORTED, "float4e2m1 weights need float8e8m0 scales with group size 32 (MXFP4)");
+    if (d->c_dtype != HM_BF16) return fail(HM_ERR_UNSUPPORTED, "MXFP4 weights are computed in bfloat16 (c_dtype must be bfloat16)");
+    if (d->has_zp) return fail(HM_ERR_INVALID, "floating-point weights have no zero point");
+  } else if (d->b_dtype == HM_UINT(4) || d->b_dtype == HM_INT(4)) {
     if (d->b_dtype == HM_INT(4) && d->has_zp) return fail(HM_ERR_INVALID, "dynamic zero point needs an unsigned weight dtype");
-    if (d->c_dtype != d->a_dtype) return fail(HM_ERR_UNSUPPORTED, "c_dtype must equal a_dtype for 16-bit activations");
-    if (d->bs_dtype != d->a_dtype) return fail(HM_ERR_UNSUPPORTED, "bs_dtype must equal a_dtype for 16-bit activations");
+    if (d->bs_dtype != d->c_dtype) return fail(HM_ERR_UNSUPPORTED, "bs_dtype must equal the 16-bit compute type (c_dtype)");
     if (g != 64 && g % hm::kStageK != 0) return fail(HM_ERR_UNSUPPORTED, "group_size=%d must be 64 or a multiple of 128", g);
   } else {
-    return fail(HM_ERR_UNSUPPORTED, "a_dtype code %d not built", d->a_dtype);
+    return fail(HM_ERR_UNSUPPORTED, "weight dtype code 0x%x not built (uint4, int4, float4e2m1)", d->b_dtype);
   }
   if (d->m_tile != 0 && d->m_tile != 16 && d->m_tile != 32 && d->m_tile != 64 && d->m_tile != 128 && d->m_tile != 192 &&
       d->m_tile != 256)
@@ -117,6 +124,8 @@ int make_plan(const hm_gemm_desc* d, int64_t m, hm_plan* plan) {
   const int64_t units = tiles * plan->kb_per_tile;
   if (units >= (1ll << 31)) return fail(HM_ERR_INVALID, "problem too large for 32-bit unit indices");
   plan->total_units = units;
+  // 8-bit activations are widened into the tail of the workspace first.
+  const int64_t act16_bytes = d->a_dtype == HM_E4M3 ? ((m * d->shape_k * 2 + 255) / 256) * 256 : 0;
   if (tiles == 0) {
     plan->grid = 0;
     plan->workspace_bytes = 256;
@@ -126,7 +135,7 @@ int make_plan(const hm_gemm_desc* d, int64_t m, hm_plan* plan) {
     plan->mode = 0;
     plan->grid = static_cast<int32_t>(tiles < sms ? tiles : sms);
     plan->units_per_cta = 0;
-    plan->workspace_bytes = 256;
+    plan->workspace_bytes = 256 + act16_bytes;
   } else {
     plan->mode = 1;
     const int64_t min_units = 2;  // do not cut work finer than two 128-K steps per CTA
@@ -138,7 +147,7 @@ int make_plan(const hm_gemm_desc* d, int64_t m, hm_plan* plan) {
     plan->grid = static_cast<int32_t>(grid);
     plan->units_per_cta = static_cast<int32_t>(per);
     int64_t counters = ((tiles * 4 * 4 + 255) / 256) * 256;
-    plan->workspace_bytes = 256 + counters + grid * 2 * static_cast<int64_t>(mt) * hm::kTileN * 4;
+    plan->workspace_bytes = 256 + counters + grid * 2 * static_cast<int64_t>(mt) * hm::kTileN * 4 + act16_bytes;
   }
   return HM_OK;
 }
@@ -155,10 +164,10 @@ hm::SchedParams sched_of(const hm_plan& pl) {
   return s;
 }
 
-template <int MT, bool BF16, bool HAS_ZP, bool A_TMEM>
+template <int MT, bool BF16, bool HAS_ZP, bool A_TMEM, int WFMT = 0>
 int launch_gemm(const hm::GemmParams& p, const CUtensorMap& tmap, int grid, cudaStream_t stream) {
   using Cfg = hm::GemmCfg<MT, A_TMEM>;
-  auto kern = hm::gemm_w4a16_kernel<MT, BF16, HAS_ZP, A_TMEM>;
+  auto kern = hm::gemm_w4a16_kernel<MT, BF16, HAS_ZP, A_TMEM, false, WFMT>;
   static bool configured[64] = {false};
   int dev = 0;
   HM_CUDA_OK(cudaGetDevice(&dev));
@@ -172,8 +181,12 @@ int launch_gemm(const hm::GemmParams& p, const CUtensorMap& tmap, int grid, cuda
 }
 
 template <int MT>
-int dispatch_gemm(bool bf16, bool zp, bool a_tmem, const hm::GemmParams& p, const CUtensorMap& tmap, int grid,
+int dispatch_gemm(bool bf16, bool zp, bool a_tmem, int wfmt, const hm::GemmParams& p, const CUtensorMap& tmap, int grid,
                   cudaStream_t stream) {
+  if (wfmt == 1) {
+    if (!a_tmem) return fail(HM_ERR_UNSUPPORTED, "MXFP4 has no shared-memory operand variant");
+    return launch_gemm<MT, true, false, true, 1>(p, tmap, grid, stream);
+  }
   if (a_tmem) {
     if (bf16) return zp ? launch_gemm<MT, true, true, true>(p, tmap, grid, stream) : launch_gemm<MT, true, false, true>(p, tmap, grid, stream);
     return zp ? launch_gemm<MT, false, true, true>(p, tmap, grid, stream) : launch_gemm<MT, false, false, true>(p, tmap, grid, stream);
@@ -253,8 +266,13 @@ int hm_repack_scale(const hm_gemm_desc* desc, const void* scales, void* out, voi
   const int groups = desc->shape_k / g;
   const int64_t total = e * desc->shape_n * groups;
   auto s = static_cast<cudaStream_t>(stream);
-  hm::repack_scale_kernel<uint16_t><<<blocks_for(total, 256), 256, 0, s>>>(
-      static_cast<const uint16_t*>(scales), static_cast<uint16_t*>(out), total, desc->shape_n, groups);
+  if (desc->bs_dtype == HM_E8M0) {
+    hm::repack_scale_kernel<uint8_t><<<blocks_for(total, 256), 256, 0, s>>>(
+        static_cast<const uint8_t*>(scales), static_cast<uint8_t*>(out), total, desc->shape_n, groups);
+  } else {
+    hm::repack_scale_kernel<uint16_t><<<blocks_for(total, 256), 256, 0, s>>>(
+        static_cast<const uint16_t*>(scales), static_cast<uint16_t*>(out), total, desc->shape_n, groups);
+  }
   HM_CUDA_OK(cudaGetLastError());
   return HM_OK;
 }
@@ -283,15 +301,16 @@ int hm_dequant_prepared(const hm_gemm_desc* desc, const void* w, const void* w_s
   if (desc->has_zp && w_zp == nullptr) return fail(HM_ERR_INVALID, "w_zp is NULL but the descriptor has zero points");
   const int g = desc->group_size == 0 ? desc->shape_k : desc->group_size;
   const int groups = desc->shape_k / g;
-  const int kbpg = g / hm::kBlockK;
+  const int kbpg = g >= hm::kBlockK ? g / hm::kBlockK : 1;
   const int64_t total = e * desc->shape_n * (desc->shape_k / hm::kBlockK);
   auto s = static_cast<cudaStream_t>(stream);
   const unsigned blocks = blocks_for(total, 128);
   auto W = static_cast<const uint8_t*>(w);
   auto S = static_cast<const uint8_t*>(w_scale);
   auto Z = static_cast<const uint8_t*>(w_zp);
-  const bool bf16 = desc->a_dtype == HM_BF16;
-  if (bf16 && desc->has_zp) hm::dequant_prepared_w4a16_kernel<true, true><<<blocks, 128, 0, s>>>(W, S, Z, out, total, desc->shape_n, desc->shape_k, groups, kbpg);
+  const bool bf16 = desc->c_dtype == HM_BF16;
+  if (desc->b_dtype == HM_E2M1) hm::dequant_prepared_mxfp4_kernel<<<blocks, 128, 0, s>>>(W, S, out, total, desc->shape_n, desc->shape_k);
+  else if (bf16 && desc->has_zp) hm::dequant_prepared_w4a16_kernel<true, true><<<blocks, 128, 0, s>>>(W, S, Z, out, total, desc->shape_n, desc->shape_k, groups, kbpg);
   else if (bf16) hm::dequant_prepared_w4a16_kernel<true, false><<<blocks, 128, 0, s>>>(W, S, Z, out, total, desc->shape_n, desc->shape_k, groups, kbpg);
   else if (desc->has_zp) hm::dequant_prepared_w4a16_kernel<false, true><<<blocks, 128, 0, s>>>(W, S, Z, out, total, desc->shape_n, desc->shape_k, groups, kbpg);
   else hm::dequant_prepared_w4a16_kernel<false, false><<<blocks, 128, 0, s>>>(W, S, Z, out, total, desc->shape_n, desc->shape_k, groups, kbpg);
@@ -356,12 +375,14 @@ int hm_gemm(const hm_gemm_desc* desc, int64_t m, const void* a, int64_t lda, con
   int rc = make_plan(desc, m, &pl);
   if (rc != HM_OK) return rc;
   if (m == 0) return HM_OK;
-  (void)a_scale;
+  const bool a_fp8 = desc->a_dtype == HM_E4M3;
+  const int wfmt = desc->b_dtype == HM_E2M1 ? 1 : 0;
   if (a == nullptr || w == nullptr || w_scale == nullptr || c == nullptr) return fail(HM_ERR_INVALID, "NULL pointer");
+  if (a_fp8 && a_scale == nullptr) return fail(HM_ERR_INVALID, "e4m3 activations need per-token scales (a_scale)");
   if (desc->has_zp && w_zp == nullptr) return fail(HM_ERR_INVALID, "w_zp is NULL but the descriptor has zero points");
   if (desc->has_bias && bias == nullptr) return fail(HM_ERR_INVALID, "bias is NULL but the descriptor has a bias");
   if (lda < desc->shape_k || ldc < desc->shape_n) return fail(HM_ERR_INVALID, "lda/ldc smaller than the row length");
-  if ((reinterpret_cast<uintptr_t>(a) & 15) || ((lda * 2) & 15)) return fail(HM_ERR_INVALID, "activations must be 16-byte aligned with a 16-byte row pitch");
+  if ((reinterpret_cast<uintptr_t>(a) & 15) || ((lda * (a_fp8 ? 1 : 2)) & 15)) return fail(HM_ERR_INVALID, "activations must be 16-byte aligned with a 16-byte row pitch");
   if ((reinterpret_cast<uintptr_t>(c) & 15) || (ldc & 7)) return fail(HM_ERR_INVALID, "output must be 16-byte aligned with a 16-byte row pitch");
   if ((reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(w_scale) & 15) || (reinterpret_cast<uintptr_t>(w_zp) & 15))
     return fail(HM_ERR_INVALID, "prepared weight buffers must be 16-byte aligned");
@@ -372,7 +393,21 @@ int hm_gemm(const hm_gemm_desc* desc, int64_t m, const void* a, int64_t lda, con
   auto encode = tensor_map_encoder();
   if (encode == nullptr) return fail(HM_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   CUtensorMap tmap;
-  const bool bf16 = desc->a_dtype == HM_BF16;
+  const bool bf16 = desc->c_dtype == HM_BF16;  // the 16-bit compute type
+  if (a_fp8) {
+    // Widen the e4m3 activations (exactly) into the tail of the workspace; the
+    // per-token scale is applied to the accumulators in the epilogue.
+    const int64_t act16_bytes = ((m * desc->shape_k * 2 + 255) / 256) * 256;
+    auto dst = reinterpret_cast<uint16_t*>(static_cast<uint8_t*>(workspace) + pl.workspace_bytes - act16_bytes);
+    const unsigned blocks = blocks_for(m * desc->shape_k / 8, 256);
+    auto src = static_cast<const uint8_t*>(a);
+    auto cs = static_cast<cudaStream_t>(stream);
+    if (bf16) hm::cvt_e4m3_to_16_kernel<true><<<blocks, 256, 0, cs>>>(src, lda, dst, m, desc->shape_k);
+    else hm::cvt_e4m3_to_16_kernel<false><<<blocks, 256, 0, cs>>>(src, lda, dst, m, desc->shape_k);
+    HM_CUDA_OK(cudaGetLastError());
+    a = dst;
+    lda = desc->shape_k;
+  }
   const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(desc->shape_k), static_cast<cuuint64_t>(m)};
   const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(lda) * 2};
   const cuuint32_t box[2] = {static_cast<cuuint32_t>(hm::kBlockK), static_cast<cuuint32_t>(pl.m_tile)};
@@ -402,20 +437,21 @@ int hm_gemm(const hm_gemm_desc* desc, int64_t m, const void* a, int64_t lda, con
   p.ldc = static_cast<int>(ldc);
   p.groups = desc->shape_k / g;
   p.steps_per_group = g >= hm::kStageK ? g / hm::kStageK : 1;
-  p.groups_per_step = g >= hm::kStageK ? 1 : hm::kStageK / g;
+  p.groups_per_step = g >= hm::kStageK ? 1 : (wfmt == 1 ? 1 : hm::kStageK / g);
   p.sched = sched_of(pl);
   p.trace = g_trace;
   p.dbg = g_dbg;
+  p.act_scale = a_fp8 ? a_scale : nullptr;
 
   const bool a_tmem = !(desc->flags & HM_FLAG_A_OPERAND_SMEM);
   auto s = static_cast<cudaStream_t>(stream);
   switch (pl.m_tile) {
-    case 16: return dispatch_gemm<16>(bf16, desc->has_zp != 0, a_tmem, p, tmap, pl.grid, s);
-    case 32: return dispatch_gemm<32>(bf16, desc->has_zp != 0, a_tmem, p, tmap, pl.grid, s);
-    case 64: return dispatch_gemm<64>(bf16, desc->has_zp != 0, a_tmem, p, tmap, pl.grid, s);
-    case 128: return dispatch_gemm<128>(bf16, desc->has_zp != 0, a_tmem, p, tmap, pl.grid, s);
-    case 192: return dispatch_gemm<192>(bf16, desc->has_zp != 0, a_tmem, p, tmap, pl.grid, s);
-    case 256: return dispatch_gemm<256>(bf16, desc->has_zp != 0, a_tmem, p, tmap, pl.grid, s);
+    case 16: return dispatch_gemm<16>(bf16, desc->has_zp != 0, a_tmem, wfmt, p, tmap, pl.grid, s);
+    case 32: return dispatch_gemm<32>(bf16, desc->has_zp != 0, a_tmem, wfmt, p, tmap, pl.grid, s);
+    case 64: return dispatch_gemm<64>(bf16, desc->has_zp != 0, a_tmem, wfmt, p, tmap, pl.grid, s);
+    case 128: return dispatch_gemm<128>(bf16, desc->has_zp != 0, a_tmem, wfmt, p, tmap, pl.grid, s);
+    case 192: return dispatch_gemm<192>(bf16, desc->has_zp != 0, a_tmem, wfmt, p, tmap, pl.grid, s);
+    case 256: return dispatch_gemm<256>(bf16, desc->has_zp != 0, a_tmem, wfmt, p, tmap, pl.grid, s);
   }
   return fail(HM_ERR_INVALID, "no kernel for m_tile=%d", pl.m_tile);
 }
@@ -446,10 +482,17 @@ int validate_moe(const hm_gemm_desc* d, int64_t capacity, int* mt_out) {
   return HM_OK;
 }
 
-int64_t moe_workspace_bytes(const hm_gemm_desc* d, int64_t capacity, int mt, int sms) {
+// Bytes before the widened-activation area (status + counters + partial slots).
+int64_t moe_core_bytes(const hm_gemm_desc* d, int64_t capacity, int mt, int sms) {
   const int64_t tiles = capacity / mt * (d->shape_n / hm::kTileN);
   const int64_t counters = ((tiles * 16 + 255) / 256) * 256;
   return 256 + counters + static_cast<int64_t>(sms) * 2 * mt * hm::kTileN * 4;
+}
+// e4m3 activations are widened to the 16-bit compute type in the workspace tail;
+// at most `capacity` rows can be referenced by sorted_ids.
+int64_t moe_workspace_bytes(const hm_gemm_desc* d, int64_t capacity, int mt, int sms) {
+  const int64_t act16 = d->a_dtype == HM_E4M3 ? ((capacity * d->shape_k * 2 + 255) / 256) * 256 : 0;
+  return moe_core_bytes(d, capacity, mt, sms) + act16;
 }
 
 template <int MT, bool BF16, bool HAS_ZP>
@@ -511,8 +554,8 @@ size_t hm_moe_gemm_workspace_bytes(const hm_gemm_desc* desc, int64_t capacity) {
   return static_cast<size_t>(moe_workspace_bytes(desc, capacity, mt, sms));
 }
 
-int hm_moe_gemm(const hm_gemm_desc* desc, int64_t num_valid, const void* a, int64_t lda, const void* w,
-                const void* w_scale, const void* w_zp, const void* bias, const float* topk_weights,
+int hm_moe_gemm(const hm_gemm_desc* desc, int64_t num_valid, const void* a, int64_t lda, const float* a_scale,
+                const void* w, const void* w_scale, const void* w_zp, const void* bias, const float* topk_weights,
                 const int32_t* sorted_ids, int64_t capacity, const int32_t* expert_ids,
                 const int32_t* num_post_padded, void* c, int64_t ldc, void* workspace, size_t workspace_bytes,
                 void* stream) {
@@ -528,8 +571,11 @@ int hm_moe_gemm(const hm_gemm_desc* desc, int64_t num_valid, const void* a, int6
   if (desc->has_zp && w_zp == nullptr) return fail(HM_ERR_INVALID, "w_zp is NULL but the descriptor has zero points");
   if (desc->has_bias && bias == nullptr) return fail(HM_ERR_INVALID, "bias is NULL but the descriptor has a bias");
   if (desc->is_moe_down && topk_weights == nullptr) return fail(HM_ERR_INVALID, "the down projection needs topk_weights");
+  if (desc->b_dtype == HM_E2M1) return fail(HM_ERR_UNSUPPORTED, "MXFP4 weights are not built for the MoE GEMM");
+  const bool a_fp8 = desc->a_dtype == HM_E4M3;
+  if (a_fp8 && a_scale == nullptr) return fail(HM_ERR_INVALID, "e4m3 activations need per-row scales (a_scale)");
   if (lda < desc->shape_k || ldc < desc->shape_n) return fail(HM_ERR_INVALID, "lda/ldc smaller than the row length");
-  if ((reinterpret_cast<uintptr_t>(a) & 15) || (lda & 7) || (reinterpret_cast<uintptr_t>(c) & 15) || (ldc & 7))
+  if ((reinterpret_cast<uintptr_t>(a) & 15) || ((lda * (a_fp8 ? 1 : 2)) & 15) || (reinterpret_cast<uintptr_t>(c) & 15) || (ldc & 7))
     return fail(HM_ERR_INVALID, "activations and output must be 16-byte aligned with 16-byte row pitches");
   if ((reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(w_scale) & 15) || (reinterpret_cast<uintptr_t>(w_zp) & 15))
     return fail(HM_ERR_INVALID, "prepared weight buffers must be 16-byte aligned");
@@ -581,8 +627,21 @@ int hm_moe_gemm(const hm_gemm_desc* desc, int64_t num_valid, const void* a, int6
   p.num_valid = static_cast<int>(num_valid);
   p.max_m_tiles = static_cast<int>(capacity / mt);
   p.min_units = 2;
-  const bool bf16 = desc->a_dtype == HM_BF16;
+  const bool bf16 = desc->c_dtype == HM_BF16;
   auto s = static_cast<cudaStream_t>(stream);
+  if (a_fp8) {
+    const int64_t rows = desc->is_moe_down ? num_valid : num_valid / desc->top_k;
+    if (rows > capacity) return fail(HM_ERR_WORKSPACE, "more activation rows than the workspace was sized for");
+    auto dst = reinterpret_cast<uint16_t*>(ws + moe_core_bytes(desc, capacity, mt, sms));
+    const unsigned blocks = blocks_for(rows * desc->shape_k / 8, 256);
+    auto src = static_cast<const uint8_t*>(a);
+    if (bf16) hm::cvt_e4m3_to_16_kernel<true><<<blocks, 256, 0, s>>>(src, lda, dst, rows, desc->shape_k);
+    else hm::cvt_e4m3_to_16_kernel<false><<<blocks, 256, 0, s>>>(src, lda, dst, rows, desc->shape_k);
+    HM_CUDA_OK(cudaGetLastError());
+    p.a = dst;
+    p.lda = desc->shape_k;
+    p.act_scale = a_scale;
+  }
   switch (mt) {
     case 16: return dispatch_moe<16>(bf16, desc->has_zp != 0, p, sms, s);
     case 32: return dispatch_moe<32>(bf16, desc->has_zp != 0, p, sms, s);

@@ -55,6 +55,28 @@ HM_DEVICE void dequant_word_u4(uint32_t w, uint32_t zp_magic2, uint32_t scale2, 
   }
 }
 
+// FP4 e2m1 codes with a power-of-two (UE8M0) group scale, decoded to bf16.
+// The 3 magnitude bits (e1 e0 m) are placed at bf16 bits 8..6 and the sign at
+// bit 15; read as bf16 that is value * 2^-126 (exponent field = e1e0, top
+// mantissa bit = m, subnormal for e1e0 = 0), so one multiply by 2^126 rebiases
+// it and a second one applies the group scale -- both exact.  Same idea as the
+// reference's shift + exponent-offset decode
+// (humming/include/humming/datatype/dequant_single.cuh:83-107,
+// kernel/dequant_weight.cuh:16-40).
+HM_DEVICE void dequant_word_e2m1_bf16(uint32_t w, uint32_t scale2, uint32_t* out4) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t t = w >> (4 * i);
+    const uint32_t r = ((t << 6) & 0x01C001C0u) | ((t << 12) & 0x80008000u);
+    out4[i] = mul2<true>(mul2<true>(r, 0x7E807E80u), scale2);  // 0x7E80 = 2^126
+  }
+}
+// bf16 bit pattern of 2^(code - 127) for a UE8M0 code (code 0 is the bf16 subnormal 2^-127).
+HM_DEVICE uint32_t e8m0_to_bf16_pair(uint32_t code) {
+  const uint32_t h = code == 0 ? 0x0040u : (code << 7);
+  return h | (h << 16);
+}
+
 template <bool BF16>
 HM_DEVICE uint32_t zp_magic_pair(uint32_t zp) {
   uint32_t h = (Magic<BF16>::kBase & 0xFFFFu) | zp;

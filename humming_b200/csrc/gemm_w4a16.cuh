@@ -87,6 +87,8 @@ struct GemmParams {
   int num_valid;               // tokens * top_k; ids >= num_valid are padding
   int max_m_tiles;             // capacity of sorted_ids in token tiles
   int min_units;               // smallest K-split worth a CTA
+  // ---- 8-bit activations (converted to the 16-bit compute type beforehand) ----
+  const float* act_scale;      // per activation row fp32 scale, multiplied into the output, or null
 };
 
 template <int MT, bool A_TMEM>
@@ -185,7 +187,9 @@ struct Ring {
 // by id and the down projection multiplies by the routing weight.  The number
 // of token tiles is a device scalar, so the K-split schedule is derived on the
 // device.
-template <int MT, bool BF16, bool HAS_ZP, bool A_TMEM, bool MOE = false>
+// WFMT: 0 = 4-bit integer codes with 16-bit group scales (+ zero points);
+//       1 = FP4 e2m1 codes with UE8M0 scales per 32 K-elements (MXFP4), bf16 compute.
+template <int MT, bool BF16, bool HAS_ZP, bool A_TMEM, bool MOE = false, int WFMT = 0>
 __global__ void __launch_bounds__(GemmCfg<MT, A_TMEM>::THREADS, 1)
 gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
   using Cfg = GemmCfg<MT, A_TMEM>;
@@ -316,7 +320,8 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
   } else if (warp == 3) {
     // ------------------------------------------------ scale / zero-point producer
     if (lane == 0) {
-      const uint32_t scale_bytes = p.groups_per_step * kScaleBytes;
+      // MXFP4: four groups of 32 per step, one scale byte per row and group.
+      const uint32_t scale_bytes = WFMT == 1 ? 4 * kTileN : p.groups_per_step * kScaleBytes;
       const uint32_t zp_bytes = p.groups_per_step * kZpBytes;
       const uint32_t tx_bytes = scale_bytes + (HAS_ZP ? zp_bytes : 0);
       Ring<SW> ring;
@@ -325,7 +330,10 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
       while (ok && iter.next(seg)) {
         // group cursor of step kb0
         int g, cnt;
-        if (p.groups_per_step == 2) {
+        if constexpr (WFMT == 1) {
+          g = 0;
+          cnt = 0;
+        } else if (p.groups_per_step == 2) {
           g = 2 * seg.kb0;
           cnt = 0;
         } else {
@@ -333,7 +341,8 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
           cnt = seg.kb0 - g * p.steps_per_group;
         }
         const size_t grp0 = expert_of(seg) * expert_groups + static_cast<size_t>(seg.n_tile) * p.groups + g;
-        const uint8_t* scales = p.w_scale + grp0 * kScaleBytes;
+        const uint8_t* scales = WFMT == 1 ? p.w_scale + (grp0 + 4 * static_cast<size_t>(seg.kb0)) * kTileN
+                                          : p.w_scale + grp0 * kScaleBytes;
         const uint8_t* zps = HAS_ZP ? p.w_zp + grp0 * kZpBytes : nullptr;
         for (int ks = seg.kb0; ks < seg.kb1; ++ks, ++it) {
           if (!mbar_wait_bounded(w_empty(ring.idx), ring.phase ^ 1, abort_flag)) {
@@ -350,7 +359,9 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
             bulk_g2s(dst + kWScaleOff, scales, scale_bytes, bar);
             if constexpr (HAS_ZP) bulk_g2s(dst + kWZpOff, zps, zp_bytes, bar);
           }
-          if (p.groups_per_step == 2) {
+          if constexpr (WFMT == 1) {
+            scales += 4 * kTileN;
+          } else if (p.groups_per_step == 2) {
             scales += 2 * kScaleBytes;
             if constexpr (HAS_ZP) zps += 2 * kZpBytes;
           } else if (++cnt == p.steps_per_group) {
@@ -574,8 +585,13 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
         codes[2] = *reinterpret_cast<const uint4*>(ws + 4096 + row * 16);
         codes[3] = *reinterpret_cast<const uint4*>(ws + 6144 + row * 16);
         uint32_t scale2[2], zpm[2];
+        uint32_t mx_scales = 0;  // MXFP4: the four group-scale bytes of this row
+        if constexpr (WFMT == 1) {
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+          for (int g4 = 0; g4 < 4; ++g4) mx_scales |= static_cast<uint32_t>(ws[kWScaleOff + g4 * kTileN + row]) << (8 * g4);
+        }
+#pragma unroll
+        for (int h = 0; h < 2 && WFMT == 0; ++h) {
           const int gi = h * half_group;
           const uint32_t sc16 = *reinterpret_cast<const uint16_t*>(ws + kWScaleOff + gi * kScaleBytes + row * 2);
           scale2[h] = sc16 | (sc16 << 16);
@@ -592,8 +608,17 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
           } else {
             const uint32_t words[8] = {codes[2 * h].x,     codes[2 * h].y,     codes[2 * h].z,     codes[2 * h].w,
                                        codes[2 * h + 1].x, codes[2 * h + 1].y, codes[2 * h + 1].z, codes[2 * h + 1].w};
+            if constexpr (WFMT == 1) {
+              static_assert(WFMT == 0 || BF16, "MXFP4 weights are decoded to bf16");
 #pragma unroll
-            for (int i = 0; i < 8; ++i) dequant_word_u4<BF16>(words[i], zpm[h], scale2[h], out + 4 * i);
+              for (int i = 0; i < 8; ++i) {  // words 0..3: group 2h, words 4..7: group 2h+1
+                const uint32_t sc = e8m0_to_bf16_pair((mx_scales >> (8 * (2 * h + (i >> 2)))) & 0xFFu);
+                dequant_word_e2m1_bf16(words[i], sc, out + 4 * i);
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) dequant_word_u4<BF16>(words[i], zpm[h], scale2[h], out + 4 * i);
+            }
           }
           if (h == 0) {
             if (q == 0 && lane == 0) trace(3 + group, it, 1);
@@ -683,14 +708,18 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
           // staging tile; then 4 lanes cover the 64 bytes of one token's 32 rows.
           int out_id = 0;      // MoE: output row of token column (c0 + lane)
           float out_w = 1.f;   // MoE down projection: its routing weight
+          float col_s = 1.f;   // 8-bit activations: the token's quantization scale
           if constexpr (MOE) {
             out_id = (lane < CH) ? p.sorted_ids[m0 + c0 + lane] : p.num_valid;
             if (p.is_down && out_id < p.num_valid) out_w = p.topk_weights[out_id];
+            if (p.act_scale != nullptr && out_id < p.num_valid) col_s = p.act_scale[p.is_down ? out_id : out_id / p.top_k];
+          } else if (p.act_scale != nullptr) {
+            if (lane < CH && c0 + lane < m_valid) col_s = p.act_scale[m0 + c0 + lane];
           }
           __syncwarp();
 #pragma unroll
           for (int j = 0; j < CH; ++j) {
-            float o = v[j] + bias;
+            float o = v[j] * __shfl_sync(0xffffffffu, col_s, j) + bias;
             if constexpr (MOE) o *= __shfl_sync(0xffffffffu, out_w, j);
             if constexpr (BF16) {
               reinterpret_cast<__nv_bfloat16*>(stage)[j * 32 + lane] = __float2bfloat16_rn(o);
@@ -765,11 +794,16 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
             for (int jj = 0; jj < 8; ++jj) {
               if (j0 + jj < m_valid) {
                 int out_row = m0 + j0 + jj;
-                float o = acc[jj] + bias;
+                float o = acc[jj];
                 if constexpr (MOE) {
                   out_row = p.sorted_ids[m0 + j0 + jj];
                   if (out_row >= p.num_valid) continue;
+                  if (p.act_scale != nullptr) o *= p.act_scale[p.is_down ? out_row : out_row / p.top_k];
+                  o += bias;
                   if (p.is_down) o *= p.topk_weights[out_row];
+                } else {
+                  if (p.act_scale != nullptr) o *= p.act_scale[out_row];
+                  o += bias;
                 }
                 store_out<BF16>(p.c, static_cast<size_t>(out_row) * p.ldc + n, o);
               }

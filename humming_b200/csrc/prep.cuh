@@ -205,6 +205,62 @@ __global__ void quant_rowwise_e4m3_kernel(const T* __restrict__ x, int64_t ldx, 
   }
 }
 
+// e4m3 activations -> the 16-bit compute type (exact), 8 elements per thread.
+template <bool BF16>
+__global__ void cvt_e4m3_to_16_kernel(const uint8_t* __restrict__ in, int64_t ld_in, uint16_t* __restrict__ out, int64_t rows,
+                                      int64_t k) {
+  const int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 8;
+  if (i >= rows * k) return;
+  const int64_t r = i / k;
+  const int64_t c = i - r * k;
+  const uint2 raw = *reinterpret_cast<const uint2*>(in + r * ld_in + c);
+  const uint8_t* b = reinterpret_cast<const uint8_t*>(&raw);
+  uint16_t o[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const __half h = __half(__nv_cvt_fp8_to_halfraw(b[j], __NV_E4M3));
+    if constexpr (BF16) {
+      const __nv_bfloat16 v = __float2bfloat16_rn(__half2float(h));
+      o[j] = *reinterpret_cast<const uint16_t*>(&v);
+    } else {
+      o[j] = *reinterpret_cast<const uint16_t*>(&h);
+    }
+  }
+  *reinterpret_cast<uint4*>(out + i) = *reinterpret_cast<const uint4*>(o);
+}
+
+// Prepared MXFP4 buffers -> fp32 (E, N, K): e2m1 codes x UE8M0 scale per 32 K.
+__global__ void dequant_prepared_mxfp4_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ w_scale,
+                                              float* __restrict__ out, int64_t total, int N, int K) {
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t >= total) return;
+  const int KB = K / kBlockK;
+  const int n_tiles = N / kTileN;
+  const int groups = K / 32;
+  const int r = static_cast<int>(t & 127);
+  int64_t rest = t >> 7;
+  const int kb = static_cast<int>(rest % KB);
+  rest /= KB;
+  const int nt = static_cast<int>(rest % n_tiles);
+  const int64_t e = rest / n_tiles;
+  const uint8_t* codes = w + ((e * n_tiles + nt) * KB + kb) * static_cast<int64_t>(kCodeBytes);
+  const uint4 lo = *reinterpret_cast<const uint4*>(codes + r * 16);
+  const uint4 hi = *reinterpret_cast<const uint4*>(codes + 2048 + r * 16);
+  const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+  uint32_t v[32];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int64_t grp = (e * n_tiles + nt) * groups + kb * 2 + (i >> 2);
+    dequant_word_e2m1_bf16(words[i], e8m0_to_bf16_pair(w_scale[grp * kTileN + r]), v + 4 * i);
+  }
+  float* dst = out + (e * N + static_cast<int64_t>(nt) * kTileN + r) * K + kb * kBlockK;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    dst[2 * i] = __uint_as_float(v[i] << 16);
+    dst[2 * i + 1] = __uint_as_float(v[i] & 0xFFFF0000u);
+  }
+}
+
 // ---- MoE block alignment (humming/utils/test.py:154-183 does this in a Python loop) ----
 // counts[e] = number of flat (token, slot) entries routed to expert e.
 __global__ void moe_count_kernel(const int* __restrict__ topk_ids, int numel, int num_experts, int* __restrict__ counts) {

@@ -68,16 +68,28 @@ class HummingLayerMeta(object):
             no("grouped input scales")
         if self.c_dtype not in (dtypes.float16, dtypes.bfloat16):
             no(f"c_dtype={self.c_dtype}")
-        if self.a_dtype in (dtypes.float16, dtypes.bfloat16):
-            if self.b_dtype not in (dtypes.uint4, dtypes.int4):
-                no(f"b_dtype={self.b_dtype} with 16-bit activations")
-            if self.c_dtype != self.a_dtype or self.bs_dtype != self.a_dtype:
-                no("c_dtype / bs_dtype different from a 16-bit a_dtype")
-            g = self.weight_scale_group_size or self.shape_k
+        sixteen = (dtypes.float16, dtypes.bfloat16)
+        if self.a_dtype not in sixteen and self.a_dtype != dtypes.float8e4m3:
+            no(f"a_dtype={self.a_dtype}")
+        if self.a_dtype in sixteen and self.c_dtype != self.a_dtype:
+            no("c_dtype different from a 16-bit a_dtype")
+        g = self.weight_scale_group_size or self.shape_k
+        if self.b_dtype == dtypes.float4e2m1:
+            if self.bs_dtype != dtypes.float8e8m0 or g != 32:
+                no("float4e2m1 weights without float8e8m0 scales of group size 32")
+            if self.c_dtype != dtypes.bfloat16:
+                no("float4e2m1 weights with a c_dtype other than bfloat16")
+            if self.num_experts is not None:
+                no("float4e2m1 weights in a MoE layer")
+        elif self.b_dtype in (dtypes.uint4, dtypes.int4):
+            if self.bs_dtype != self.c_dtype:
+                no("bs_dtype different from the 16-bit compute type (c_dtype)")
             if g != 64 and g % 128:
                 no(f"weight_scale_group_size={g} (64 or multiples of 128 only)")
         else:
-            no(f"a_dtype={self.a_dtype}")
+            no(f"b_dtype={self.b_dtype}")
+        if self.has_input_scale is False and self.a_dtype == dtypes.float8e4m3:
+            no("float8e4m3 activations without input scales")
         if self.shape_n % 128 or self.shape_k % 128:
             no("shape_n or shape_k not a multiple of 128")
         if self.has_dynamic_zp and self.b_dtype.is_signed:
@@ -372,10 +384,12 @@ class HummingMethod(torch.nn.Module):
         if not layer.humming_prepared[sublayer_name]:
             raise RuntimeError("call finish_load before forward")
         if meta.num_experts is not None:
-            return cls._forward_moe(layer, meta, inputs, outputs, topk_weights, sorted_token_ids, expert_ids,
+            return cls._forward_moe(layer, meta, inputs, outputs, input_scale, topk_weights, sorted_token_ids, expert_ids,
                                     num_tokens_post_padded, sublayer_name)
         if sorted_token_ids is not None:
             raise ValueError("routing tensors given to a dense layer")
+        if meta.a_dtype.num_bits != 16 and inputs.dtype in _FLOAT_DTYPES:
+            input_scale = None  # unquantized activations: quantize them here (dynamic per-token scales)
         inputs, input_scale = cls.may_quant_input(meta, inputs, input_scale)
         a = inputs.reshape(-1, inputs.size(-1))
         if a.stride(-1) != 1 or (a.stride(0) * a.element_size()) % 16 or a.data_ptr() % 16:
@@ -385,6 +399,10 @@ class HummingMethod(torch.nn.Module):
             raise ValueError(f"inputs have K={a.size(1)}, layer expects {meta.shape_k}")
         if a.dtype != dtypes.torch_dtype_map[meta.a_dtype]:
             raise ValueError(f"inputs are {a.dtype}, layer expects {meta.a_dtype}")
+        if input_scale is not None:
+            input_scale = input_scale.reshape(-1).float().contiguous()
+            if input_scale.numel() != m:
+                raise ValueError("input_scale must hold one fp32 scale per token")
 
         m_tile = 0
         cfg = layer.humming_block_size_configs[sublayer_name]
@@ -422,7 +440,7 @@ class HummingMethod(torch.nn.Module):
         raise RuntimeError("no MoE block-size table: call prepare_default_kernel_configs(layer, is_moe=True, top_k=...)")
 
     @classmethod
-    def _forward_moe(cls, layer, meta, inputs, outputs, topk_weights, sorted_token_ids, expert_ids,
+    def _forward_moe(cls, layer, meta, inputs, outputs, input_scale, topk_weights, sorted_token_ids, expert_ids,
                      num_tokens_post_padded, sublayer_name):
         """Indexed GEMM over the experts (reference docs/CONFIG.md "MoE Config"):
         up projection reads row ``id // top_k`` of ``inputs (M, K)``, down projection row
@@ -438,9 +456,16 @@ class HummingMethod(torch.nn.Module):
         if is_down and topk_weights is None:
             raise ValueError("the down projection needs topk_weights")
         num_tokens = inputs.size(0)
+        if meta.a_dtype.num_bits != 16 and inputs.dtype in _FLOAT_DTYPES:
+            input_scale = None
+        inputs, input_scale = cls.may_quant_input(meta, inputs, input_scale)
         a = inputs.reshape(-1, inputs.size(-1))
         if a.stride(-1) != 1 or (a.stride(0) * a.element_size()) % 16 or a.data_ptr() % 16:
             a = a.contiguous()
+        if input_scale is not None:
+            input_scale = input_scale.reshape(-1).float().contiguous()
+            if input_scale.numel() != a.size(0):
+                raise ValueError("input_scale must hold one fp32 scale per activation row")
         if a.size(1) != meta.shape_k or a.size(0) != num_tokens * (top_k if is_down else 1):
             raise ValueError(f"inputs of shape {tuple(inputs.shape)} do not fit a "
                              f"{'down' if is_down else 'up'} projection with K={meta.shape_k}, top_k={top_k}")
@@ -463,7 +488,7 @@ class HummingMethod(torch.nn.Module):
         runtime.moe_gemm(desc, num_tokens * top_k, a, getattr(layer, meta.weight_name),
                          getattr(layer, meta.weight_scale_name, None), getattr(layer, meta.zero_point_name, None),
                          getattr(layer, meta.bias_name, None), tkw, ids.contiguous(), expert_ids.int().contiguous(),
-                         num_tokens_post_padded.reshape(-1).int(), outputs.view(-1, meta.shape_n), ws)
+                         num_tokens_post_padded.reshape(-1).int(), outputs.view(-1, meta.shape_n), ws, a_scale=input_scale)
         return outputs
 
     @classmethod

@@ -57,7 +57,7 @@ SIGNATURES = {
     "hm_gemm": (_I, [_DESC, _L, _P, _L, _P, _P, _P, _P, _P, _P, _L, _P, ctypes.c_size_t, _P]),
     "hm_moe_align_block_size": (_I, [_P, _L, _I, _I, _P, _L, _P, _P, _P, _P]),
     "hm_moe_gemm_workspace_bytes": (ctypes.c_size_t, [_DESC, _L]),
-    "hm_moe_gemm": (_I, [_DESC, _L, _P, _L, _P, _P, _P, _P, _P, _P, _L, _P, _P, _P, _L, _P, ctypes.c_size_t, _P]),
+    "hm_moe_gemm": (_I, [_DESC, _L, _P, _L, _P, _P, _P, _P, _P, _P, _P, _L, _P, _P, _P, _L, _P, ctypes.c_size_t, _P]),
     "hm_moe_route": (_I, [_P, _L, _I, _I, _I, _I, _P, _P, _P]),
     "hm_silu_mul": (_I, [_P, _P, _L, _I, _I, _P]),
     "hm_topk_sum": (_I, [_P, _P, _L, _I, _I, _I, _P]),

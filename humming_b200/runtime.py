@@ -177,12 +177,12 @@ def moe_workspace_bytes(desc: native.GemmDesc, capacity: int) -> int:
 
 
 def moe_gemm(desc: native.GemmDesc, num_valid: int, a, w, w_scale, w_zp, bias, topk_weights, sorted_ids, expert_ids,
-             num_post_padded, c, workspace):
+             num_post_padded, c, workspace, a_scale=None):
     """Enqueue one indexed (MoE) GEMM on the current stream of ``a``'s device."""
-    _require_cuda(a, w, w_scale, w_zp, bias, topk_weights, sorted_ids, expert_ids, num_post_padded, c, workspace)
+    _require_cuda(a, w, w_scale, w_zp, bias, topk_weights, sorted_ids, expert_ids, num_post_padded, c, workspace, a_scale)
     with torch.cuda.device(a.device):
         native.check(native.lib.hm_moe_gemm(
-            ctypes.byref(desc), num_valid, _ptr(a), a.stride(0), _ptr(w), _ptr(w_scale), _ptr(w_zp), _ptr(bias),
+            ctypes.byref(desc), num_valid, _ptr(a), a.stride(0), _ptr(a_scale), _ptr(w), _ptr(w_scale), _ptr(w_zp), _ptr(bias),
             _ptr(topk_weights), _ptr(sorted_ids), sorted_ids.numel(), _ptr(expert_ids), _ptr(num_post_padded), _ptr(c),
             c.stride(0), _ptr(workspace), workspace.nelement() * workspace.element_size(), _stream(a.device)))
     return c

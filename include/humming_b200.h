@@ -55,10 +55,10 @@ enum {
 typedef struct hm_gemm_desc {
   int32_t shape_n;
   int32_t shape_k;
-  int32_t a_dtype;      /* HM_F16 | HM_BF16 | HM_E4M3                               */
-  int32_t b_dtype;      /* HM_UINT(4) | HM_INT(4) | HM_E2M1 ...                     */
+  int32_t a_dtype;      /* HM_F16 | HM_BF16 | HM_E4M3 (per-token fp32 scales)       */
+  int32_t b_dtype;      /* HM_UINT(4) | HM_INT(4) | HM_E2M1 (with HM_E8M0, group 32) */
   int32_t c_dtype;      /* HM_F16 | HM_BF16                                         */
-  int32_t bs_dtype;     /* HM_F16 | HM_BF16 | HM_F32 | HM_E8M0                      */
+  int32_t bs_dtype;     /* = c_dtype for integer weights; HM_E8M0 for HM_E2M1        */
   int32_t group_size;   /* weight-scale group along K; 0 = one scale per row        */
   int32_t has_zp;       /* dynamic zero points (same groups as the scales)          */
   int32_t has_bias;
@@ -182,11 +182,12 @@ HM_API size_t hm_moe_gemm_workspace_bytes(const hm_gemm_desc* desc, int64_t capa
  * a is (tokens * top_k, K), row id is read and the result is multiplied by
  * topk_weights[id] (fp32).  Row id of c (tokens * top_k, shape_n) is written for
  * every id < num_valid = tokens * top_k; padding entries are skipped.
+ * a_scale: one fp32 scale per row of a for e4m3 activations, else NULL.
  * w / w_scale / w_zp: prepared buffers with a leading expert dimension.
  * Replaces launch_humming with is_moe (humming/csrc/launcher/launcher.cpp:61-161,
  * humming/include/humming/scheduler.cuh:158-182, docs/CONFIG.md "MoE Config"). */
-HM_API int hm_moe_gemm(const hm_gemm_desc* desc, int64_t num_valid, const void* a, int64_t lda, const void* w,
-                       const void* w_scale, const void* w_zp, const void* bias, const float* topk_weights,
+HM_API int hm_moe_gemm(const hm_gemm_desc* desc, int64_t num_valid, const void* a, int64_t lda, const float* a_scale,
+                       const void* w, const void* w_scale, const void* w_zp, const void* bias, const float* topk_weights,
                        const int32_t* sorted_ids, int64_t capacity, const int32_t* expert_ids,
                        const int32_t* num_post_padded, void* c, int64_t ldc, void* workspace, size_t workspace_bytes,
                        void* stream);

@@ -37,7 +37,10 @@ def test_version_and_error_string():
     assert native.lib.hm_gemm_plan(_desc(shape_n=1000), 16, plan) == native.HM_ERR_INVALID
     assert "128" in native.last_error()
     assert native.lib.hm_gemm_plan(_desc(b_dtype=0x103), 16, plan) == native.HM_ERR_UNSUPPORTED
-    assert native.lib.hm_gemm_plan(_desc(a_dtype=4), 16, plan) == native.HM_ERR_UNSUPPORTED
+    assert native.lib.hm_gemm_plan(_desc(a_dtype=5), 16, plan) == native.HM_ERR_UNSUPPORTED        # e5m2 activations
+    assert native.lib.hm_gemm_plan(_desc(a_dtype=4), 16, plan) == native.HM_OK                      # e4m3 activations
+    assert native.lib.hm_gemm_plan(_desc(a_dtype=4, b_dtype=7, bs_dtype=6, group_size=32, c_dtype=2), 16, plan) == native.HM_OK
+    assert native.lib.hm_gemm_plan(_desc(a_dtype=4, b_dtype=7, bs_dtype=6, group_size=128, c_dtype=2), 16, plan) == native.HM_ERR_UNSUPPORTED
     assert native.lib.hm_gemm_plan(_desc(group_size=96), 16, plan) == native.HM_ERR_INVALID
     assert native.lib.hm_gemm_plan(_desc(m_tile=48), 16, plan) == native.HM_ERR_INVALID
     with pytest.raises(ValueError):

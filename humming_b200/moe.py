@@ -85,14 +85,18 @@ class HummingMoE(torch.nn.Module):
 
     def __init__(self, hidden_size: int, intermediate_size: int, num_experts: int, top_k: int, dtype: str = "bfloat16",
                  b_dtype: str = "uint4", weight_scale_group_size: int = 128, has_dynamic_zp: bool = False,
-                 group: Optional["dist.ProcessGroup"] = None):
+                 group: Optional["dist.ProcessGroup"] = None, a_dtype: Optional[str] = None):
+        """``a_dtype="float8e4m3"`` selects W4A8: the hidden states and the SiLU*mul output are quantized per
+        token (dynamic fp32 scales) before the up and the down GEMM; ``dtype`` stays the 16-bit type of scales,
+        intermediate results and outputs."""
         super().__init__()
         from humming_b200.layer import HummingLayer
 
         self.ep = ExpertParallel(num_experts, group)
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
         self.num_experts, self.top_k = num_experts, top_k
-        common = dict(a_dtype=dtype, b_dtype=b_dtype, c_dtype=dtype, bs_dtype=dtype, weight_scale_group_size=weight_scale_group_size,
+        self.fp8 = a_dtype is not None and str(a_dtype) == "float8e4m3"
+        common = dict(a_dtype=a_dtype or dtype, b_dtype=b_dtype, c_dtype=dtype, bs_dtype=dtype, weight_scale_group_size=weight_scale_group_size,
                       has_dynamic_zp=has_dynamic_zp, num_experts=self.ep.experts_per_rank)
         self.up = HummingLayer(shape_n=2 * intermediate_size, shape_k=hidden_size, **common)    # rows [gate | up]
         self.down = HummingLayer(shape_n=hidden_size, shape_k=intermediate_size, **common)
@@ -124,9 +128,16 @@ class HummingMoE(torch.nn.Module):
         block = HummingMethod.moe_block_size(self.up, tokens)
         sorted_ids, expert_ids, total = runtime.moe_align_block_size(local_e, self.ep.experts_per_rank, block)
         routing = dict(sorted_token_ids=sorted_ids, expert_ids=expert_ids, num_tokens_post_padded=total)
-        h = self.up(inputs=rows, **routing)                                   # (T, k, 2I)
+        if self.fp8:
+            rows, rows_scale = runtime.quant_input(rows, "float8e4m3")
+            h = self.up(inputs=rows, input_scale=rows_scale, **routing)        # (T, k, 2I)
+        else:
+            h = self.up(inputs=rows, **routing)
         act = runtime.silu_mul(h.view(tokens * top_k, 2 * self.intermediate_size))
-        out = self.down(inputs=act.view(tokens, top_k, self.intermediate_size), topk_weights=w, **routing)
+        act_scale = None
+        if self.fp8:
+            act, act_scale = runtime.quant_input(act, "float8e4m3")
+        out = self.down(inputs=act.view(tokens, top_k, self.intermediate_size), input_scale=act_scale, topk_weights=w, **routing)
         return out.view(tokens * top_k, self.hidden_size)
 
     def forward(self, hidden_states: torch.Tensor, router_logits: torch.Tensor) -> torch.Tensor:

@@ -16,7 +16,14 @@ def dequant(codes, scales):
     return ((codes.float() - 8.0) * scales.float().repeat_interleave(128, -1)).bfloat16().float()
 
 
-def moe_layer_reference(hidden_states, router_logits, weights, top_k):
+def _fake_quant_e4m3(x):
+    """Per-token dynamic e4m3 quantization followed by dequantization (fp32)."""
+    absmax = x.abs().amax(-1, keepdim=True).clamp_min(1e-30)
+    scale = absmax / 448.0
+    return (x * (1.0 / scale)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).float() * scale
+
+
+def moe_layer_reference(hidden_states, router_logits, weights, top_k, fp8=False):
     """route -> per-expert gate|up -> silu*up -> down x weight -> sum, with the
     pipeline's bf16 roundings (GEMM outputs, activation, per-slot outputs, sum)."""
     up_codes, up_scales, down_codes, down_scales = weights
@@ -25,11 +32,15 @@ def moe_layer_reference(hidden_states, router_logits, weights, top_k):
     w, ids = probs.topk(top_k, 1)
     w = w / w.sum(-1, keepdim=True)
     x = hidden_states.float()
+    if fp8:
+        x = _fake_quant_e4m3(x)
     out = torch.zeros((x.size(0), top_k, x.size(1)))
     for e in ids.unique().tolist():
         wu, wd = dequant(up_codes[e], up_scales[e]), dequant(down_codes[e], down_scales[e])
         tok, slot = torch.where(ids == e)
         h = (x[tok] @ wu.T).bfloat16().float()
         act = (torch.nn.functional.silu(h[:, :inter]) * h[:, inter:]).bfloat16().float()
+        if fp8:
+            act = _fake_quant_e4m3(act)
         out[tok, slot] = ((act @ wd.T) * w[tok, slot, None]).bfloat16().float()
     return out.sum(1).bfloat16(), ids, w

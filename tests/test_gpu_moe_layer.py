@@ -50,3 +50,22 @@ def test_moe_layer_single_gpu(cuda_device, tokens):
     moe.check_status()
     ref, _, _ = moe_layer_reference(x, logits, weights, top_k)
     torch.testing.assert_close(out.float().cpu(), ref.float(), rtol=0.05, atol=0.1)
+
+
+@pytest.mark.parametrize("tokens", [5, 200])
+def test_moe_layer_w4a8(cuda_device, tokens):
+    """int4 weights, e4m3 activations with per-token scales re-quantized between the two GEMMs."""
+    experts, top_k, hidden, inter = 8, 2, 512, 256
+    weights = make_expert_weights(experts, hidden, inter, seed=5)
+    moe = HummingMoE(hidden, inter, experts, top_k, b_dtype="int4", a_dtype="float8e4m3").to(cuda_device)
+    for e in range(experts):
+        moe.load_expert(e, (weights[0][e] - 8).to(cuda_device), weights[1][e].to(cuda_device), (weights[2][e] - 8).to(cuda_device),
+                        weights[3][e].to(cuda_device))
+    moe.finish_load()
+    gen = torch.Generator(device="cpu").manual_seed(tokens)
+    x = torch.randn((tokens, hidden), generator=gen).bfloat16()
+    logits = torch.randn((tokens, experts), generator=gen)
+    out = moe(x.to(cuda_device), logits.to(cuda_device))
+    moe.check_status()
+    ref, _, _ = moe_layer_reference(x, logits, weights, top_k, fp8=True)
+    torch.testing.assert_close(out.float().cpu(), ref.float(), rtol=0.05, atol=0.1)

@@ -131,6 +131,8 @@ int make_plan(const hm_gemm_desc* d, int64_t m, hm_plan* plan) {
     plan->workspace_bytes = 256;
     return HM_OK;
   }
+  // Token tiles up to 64 run two CTAs per SM (see GemmCfg::DUAL).
+  if (mt <= 64 && !(d->flags & HM_FLAG_A_OPERAND_SMEM)) sms *= 2;
   if ((d->flags & HM_FLAG_NO_SPLIT_K) || tiles >= 4ll * sms) {
     plan->mode = 0;
     plan->grid = static_cast<int32_t>(tiles < sms ? tiles : sms);
@@ -173,6 +175,7 @@ int launch_gemm(const hm::GemmParams& p, const CUtensorMap& tmap, int grid, cuda
   HM_CUDA_OK(cudaGetDevice(&dev));
   if (!configured[dev & 63]) {
     HM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_ALLOC));
+    HM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
     configured[dev & 63] = true;
   }
   kern<<<grid, Cfg::THREADS, Cfg::SMEM_ALLOC, stream>>>(p, tmap);
@@ -504,6 +507,7 @@ int launch_moe(const hm::GemmParams& p, int grid, cudaStream_t stream) {
   HM_CUDA_OK(cudaGetDevice(&dev));
   if (!configured[dev & 63]) {
     HM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_ALLOC));
+    HM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
     configured[dev & 63] = true;
   }
   CUtensorMap unused;
@@ -551,6 +555,7 @@ size_t hm_moe_gemm_workspace_bytes(const hm_gemm_desc* desc, int64_t capacity) {
   if (validate_moe(desc, capacity, &mt) != HM_OK) return 0;
   int sms = desc->num_sms;
   if (sms <= 0 && device_sm_count(&sms) != HM_OK) return 0;
+  if (mt <= 64) sms *= 2;  // two CTAs per SM for small token tiles
   return static_cast<size_t>(moe_workspace_bytes(desc, capacity, mt, sms));
 }
 
@@ -584,6 +589,7 @@ int hm_moe_gemm(const hm_gemm_desc* desc, int64_t num_valid, const void* a, int6
     rc = device_sm_count(&sms);
     if (rc != HM_OK) return rc;
   }
+  if (mt <= 64) sms *= 2;  // two CTAs per SM for small token tiles
   const int64_t need = moe_workspace_bytes(desc, capacity, mt, sms);
   if (workspace == nullptr || workspace_bytes < static_cast<size_t>(need))
     return fail(HM_ERR_WORKSPACE, "workspace of %zu bytes given, %lld needed", workspace_bytes, static_cast<long long>(need));

@@ -99,11 +99,17 @@ struct GemmCfg {
   // weights (64 TMEM columns, or 32 KB of shared memory in the cross-check
   // variant), SX activation stages (two 64-K boxes each, shared memory), SW
   // packed-weight stages.
-  static constexpr int SA = (!A_TMEM || MT == 192) ? 2 : 4;
+  // Token tiles up to 64 are bound by the issue rate and the latencies of the
+  // one MMA-issuing thread (>= 45-52 cycles per K=16 MMA whatever N is), not by
+  // the tensor pipe: two CTAs share an SM there (half the tensor memory, half
+  // the warps and ring slots each) so that two issue streams interleave.
+  static constexpr bool DUAL = A_TMEM && MT <= 64;
+  static constexpr int CTAS_PER_SM = DUAL ? 2 : 1;
+  static constexpr int SA = (!A_TMEM || MT == 192 || DUAL) ? 2 : 4;
   // An activation stage is released by the same tcgen05.commit as the operand
   // slot of its step (one commit per step), so its ring cannot be deeper.
   static constexpr int SX = MT <= 128 ? SA : 2;
-  static constexpr int SW = MT <= 64 ? 8 : 4;
+  static constexpr int SW = DUAL ? 4 : (MT <= 64 ? 8 : 4);
   // Dequant warp groups (4 warps each) taking stages round-robin.  A slot (and a
   // weight stage) must always be refilled by the group that filled it before:
   // phase-parity waits cannot tell a barrier that is two phases behind from one
@@ -190,7 +196,7 @@ struct Ring {
 // WFMT: 0 = 4-bit integer codes with 16-bit group scales (+ zero points);
 //       1 = FP4 e2m1 codes with UE8M0 scales per 32 K-elements (MXFP4), bf16 compute.
 template <int MT, bool BF16, bool HAS_ZP, bool A_TMEM, bool MOE = false, int WFMT = 0>
-__global__ void __launch_bounds__(GemmCfg<MT, A_TMEM>::THREADS, 1)
+__global__ void __launch_bounds__(GemmCfg<MT, A_TMEM>::THREADS, GemmCfg<MT, A_TMEM>::CTAS_PER_SM)
 gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
   using Cfg = GemmCfg<MT, A_TMEM>;
   constexpr int SX = Cfg::SX;
@@ -579,11 +585,6 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
         }
         if (q == 0 && lane == 0) trace(3 + group, it, 0);
         const uint8_t* ws = smem_gen + Cfg::SMEM_W + sw * kWStageBytes;
-        uint4 codes[4];
-        codes[0] = *reinterpret_cast<const uint4*>(ws + row * 16);
-        codes[1] = *reinterpret_cast<const uint4*>(ws + 2048 + row * 16);
-        codes[2] = *reinterpret_cast<const uint4*>(ws + 4096 + row * 16);
-        codes[3] = *reinterpret_cast<const uint4*>(ws + 6144 + row * 16);
         uint32_t scale2[2], zpm[2];
         uint32_t mx_scales = 0;  // MXFP4: the four group-scale bytes of this row
         if constexpr (WFMT == 1) {
@@ -602,12 +603,13 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           uint32_t out[32];
+          const uint4 c_lo = *reinterpret_cast<const uint4*>(ws + h * 4096 + row * 16);         // K  0..31 of this half
+          const uint4 c_hi = *reinterpret_cast<const uint4*>(ws + h * 4096 + 2048 + row * 16);  // K 32..63
           if (p.dbg & HM_DBG_SKIP_MATH) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) out[i] = codes[2 * h].x + i;
+            for (int i = 0; i < 32; ++i) out[i] = c_lo.x + i;
           } else {
-            const uint32_t words[8] = {codes[2 * h].x,     codes[2 * h].y,     codes[2 * h].z,     codes[2 * h].w,
-                                       codes[2 * h + 1].x, codes[2 * h + 1].y, codes[2 * h + 1].z, codes[2 * h + 1].w};
+            const uint32_t words[8] = {c_lo.x, c_lo.y, c_lo.z, c_lo.w, c_hi.x, c_hi.y, c_hi.z, c_hi.w};
             if constexpr (WFMT == 1) {
               static_assert(WFMT == 0 || BF16, "MXFP4 weights are decoded to bf16");
 #pragma unroll

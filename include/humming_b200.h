@@ -223,7 +223,7 @@ HM_API int hm_topk_sum(const void* x, void* out, int64_t tokens, int top_k, int 
  * library's device image (every GPU that loads the library holds that much
  * memory until the process exits).  The call allocates nothing: no cudaMalloc,
  * no cudaFree, no allocating library routine.  Shapes whose launch plan needs
- * more scratch than the array holds (roughly: more than 32 rows on large
+ * more scratch than the array holds (roughly: more than 16 rows on large
  * layers) are refused with HM_ERR_WORKSPACE and a message that states both
  * sizes; use hm_gemm with your own workspace for those.
  *

@@ -79,7 +79,7 @@ def test_schedule_covers_every_unit_exactly_once(n, k, m, flags):
     tiles = plan.n_tiles * plan.m_tiles
     kb = plan.kb_per_tile
     assert plan.total_units == tiles * kb
-    assert 1 <= plan.grid <= 148
+    assert 1 <= plan.grid <= (296 if plan.m_tile <= 64 else 148)   # two CTAs per SM for token tiles up to 64
     covered = {}
     partial_by_tile = {}
     slots = set()

@@ -183,6 +183,7 @@ def run_point(args):
                              bs_dtype="bfloat16", weight_scale_group_size=GROUP, has_dynamic_zp=True).to(dev)
         layer.load_weight(weight=case.codes.to(dev), weight_scale=case.scales.to(dev), zero_point=case.zero_points.to(dev))
         layer.finish_load()
+        layer.humming_kernel_options[""]["native_flags"] = args.native_flags
         layers.append(layer)
     x = synthetic.activations(m, k, torch.bfloat16).to(dev)
     out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
@@ -282,6 +283,7 @@ def run_ours(args, rank, world, local_rank):
                                  bs_dtype="bfloat16", weight_scale_group_size=GROUP, has_dynamic_zp=True).to(dev)
             layer.load_weight(weight=case.codes.to(dev), weight_scale=case.scales.to(dev), zero_point=case.zero_points.to(dev))
             layer.finish_load()
+            layer.humming_kernel_options[""]["native_flags"] = args.native_flags
             copies.append(layer)
         layers[name] = copies
         del case
@@ -346,8 +348,9 @@ def run_ours(args, rank, world, local_rank):
         b.record()
         torch.cuda.synchronize()
         us = a.elapsed_time(b) * 1e3 / (nrep * REP)
-        plan = runtime.gemm_plan(HummingMethod._desc(layers[name][0].meta), m)
+        plan = runtime.gemm_plan(HummingMethod._desc(layers[name][0].meta, flags=args.native_flags), m)
         per_point.append({"proj": name, "m": m, "n": n, "k": k, "us": round(us, 2), "m_tile": plan.m_tile,
+                          "cta_pair": plan.cta_pair, "k_split": plan.mode,
                           "tflops": round(gemm_flops(m, n, k) / us / 1e6, 2), "gbs": round(gemm_bytes(m, n, k) / us / 1e3, 1)})
         del g
 
@@ -417,7 +420,8 @@ def run_ours(args, rank, world, local_rank):
         "gpu_launches": len(points) * args.steps,
         "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": big_ach, "peak": peak_tc, "unit": "TFLOP/s", "frac": big_ach / peak_tc,
-                     "traffic": None, "kernel": "gemm_w4a16_kernel<256,bf16,zp,tmem> (all launches with M >= 256)",
+                     "traffic": None, "kernel": "gemm_w4a16_kernel<256,bf16,zp,tmem>, CTA-pair or single-CTA instantiation as planned "
+                               f"({sum(p['cta_pair'] for p in big)} of {len(big)} launches on the 256-token tile are CTA pairs)",
                      "peak_source": f"{peaks['source']} cuBLAS bf16, sustained", "top_launch": top},
         "roofline_decode": {"bound": "hbm", "achieved": small_ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                             "frac": small_ach / peaks["hbm_gbs"], "traffic": None,
@@ -438,6 +442,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="dense", choices=["dense", "moe"])
     ap.add_argument("--tokens", default="32,512,4096", help="moe workload: total token counts to time, the last one is the headline")
+    ap.add_argument("--native-flags", type=int, default=0, help="HM_FLAG_* bits OR-ed into every dense GEMM descriptor (kernel A/B comparisons)")
     ap.add_argument("--point", default=None, help="PROJ:M, e.g. gate_up:16 -- launch only this sweep point a few times")
     args = ap.parse_args()
 

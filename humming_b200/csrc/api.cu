@@ -97,6 +97,59 @@ int validate_desc(const hm_gemm_desc* d) {
   return HM_OK;
 }
 
+// One way to run (desc, m): token tile, one CTA or a CTA pair per weight tile,
+// whole tiles or a K split.
+struct PlanChoice {
+  int mt;
+  bool pair;
+  int mode;
+  int64_t tiles, units, grid, per;
+  double cost_us;
+};
+
+// Estimated run time of a choice, from per-step times measured on B200 with the
+// Llama-3-8B projections (4-bit codes, group 128) for M = 1 ... 8192:
+//   time = start-up + (128-K steps of the busiest worker) x (time per step)
+//          + for a K split, the fp32 partial tiles written and read back through L2.
+// It only has to rank the choices: tiles of 16-64 tokens run two CTAs per SM and
+// are bound by the MMA issue rate, whatever the tile width; 128- and 256-token
+// tiles are bound by the tensor pipe; a CTA pair halves the activation traffic
+// of the 256-token tile.
+void estimate(PlanChoice* c, const hm_gemm_desc* d, int kb, int sms) {
+  const bool smem_operand = (d->flags & HM_FLAG_A_OPERAND_SMEM) != 0;
+  const bool dual = c->mt <= 64 && !c->pair && !smem_operand;
+  const int workers = c->pair ? (sms / 2 > 0 ? sms / 2 : 1) : (dual ? 2 * sms : sms);
+  double step_us, start_us;
+  if (c->pair) {
+    // 256-token tile: the accumulator drain of each tile (about 4.5 us) is not overlapped.
+    step_us = c->mt == 256 ? 0.84 + 4.5 / kb : c->mt == 128 ? 1.40 : 1.20;
+    start_us = 3.0;
+  } else if (c->mt <= 64) {
+    step_us = c->mt == 64 ? 0.85 : 0.78;
+    start_us = 11.0;
+  } else {
+    step_us = c->mt == 128 ? 0.654 : c->mt == 192 ? 0.85 : 1.03;
+    start_us = c->mt == 128 ? 5.0 : 3.0;
+  }
+  if (c->mode == 0) {
+    c->grid = c->tiles < workers ? c->tiles : workers;
+    c->per = 0;
+    const int64_t waves = (c->tiles + c->grid - 1) / c->grid;
+    c->cost_us = start_us + static_cast<double>(waves * kb) * step_us;
+  } else {
+    const int64_t min_units = 2;  // do not cut work finer than two 128-K steps per CTA
+    int64_t max_ctas = c->units / min_units;
+    if (max_ctas < 1) max_ctas = 1;
+    int64_t grid = max_ctas < workers ? max_ctas : workers;
+    c->per = (c->units + grid - 1) / grid;
+    c->grid = (c->units + c->per - 1) / c->per;
+    const double partial_bytes = 2.0 * static_cast<double>(c->grid) * (c->pair ? 2 : 1) * 2.0 * c->mt * hm::kTileN * 4;
+    c->cost_us = start_us + static_cast<double>(c->per) * step_us + 0.5 + partial_bytes / 3.5e6;
+    // On a near tie keep whole tiles (results independent of the split); a split pair measured slower than estimated.
+    c->cost_us *= c->pair ? 1.20 : 1.03;
+  }
+}
+
 int make_plan(const hm_gemm_desc* d, int64_t m, hm_plan* plan) {
   int rc = validate_desc(d);
   if (rc != HM_OK) return rc;
@@ -106,50 +159,91 @@ int make_plan(const hm_gemm_desc* d, int64_t m, hm_plan* plan) {
     rc = device_sm_count(&sms);
     if (rc != HM_OK) return rc;
   }
-  int mt = d->m_tile;
-  if (mt == 0) {
-    // The 192-token tile (two accumulators, epilogue overlapped) measured slower
-    // than the 256-token tile (one accumulator) on B200, so it is used only on
-    // request.
-    mt = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : m <= 128 ? 128 : 256;
-  }
-  if ((d->flags & HM_FLAG_A_OPERAND_SMEM) && mt > 128)
+  const bool smem_operand = (d->flags & HM_FLAG_A_OPERAND_SMEM) != 0;
+  if (smem_operand && d->m_tile > 128)
     return fail(HM_ERR_UNSUPPORTED, "the shared-memory operand variant is built for token tiles up to 128");
+  // CTA pairs (cta_group::2): 256 weight rows per tile, token tile a multiple of 32.
+  const bool pair_ok = !smem_operand && d->b_dtype != HM_E2M1 && d->shape_n % (2 * hm::kTileN) == 0 && !(d->flags & HM_FLAG_NO_CTA_PAIR);
+  const bool pair_forced = pair_ok && (d->flags & HM_FLAG_CTA_PAIR);
+  const int kb = d->shape_k / hm::kStageK;
+
+  // Token tiles worth trying for this m.  (The 192-token tile measured slower
+  // than the 256-token one on B200 and is used only on request.)
+  int tiles_to_try[4];
+  int n_try = 0;
+  if (d->m_tile != 0) {
+    tiles_to_try[n_try++] = d->m_tile;
+  } else {
+    static const int all[5] = {16, 32, 64, 128, 256};
+    const int cap = smem_operand ? 128 : 256;
+    for (int i = 0; i < 5; ++i) {
+      const int t = all[i];
+      const bool covers = t >= m || t == cap;           // smallest tile holding all of m, or the widest
+      const bool useful = t < m && 8 * t >= (m < 256 ? m : 256);  // narrower tiles down to m/8
+      if (t <= cap && (useful || covers) && (t <= 16 || 2 * m > t) && n_try < 4) tiles_to_try[n_try++] = t;
+    }
+    if (n_try == 0) tiles_to_try[n_try++] = 16;
+    if (pair_forced) {  // the narrowest pair tile is 32 tokens
+      bool has32 = false;
+      for (int i = 0; i < n_try; ++i) has32 = has32 || tiles_to_try[i] == 32;
+      for (int i = 0; i < n_try; ++i) {
+        if (tiles_to_try[i] == 16) tiles_to_try[i] = has32 ? tiles_to_try[--n_try] : 32;
+      }
+    }
+  }
+
+  PlanChoice best;
+  best.cost_us = -1.0;
+  for (int i = 0; i < n_try; ++i) {
+    const int mt = tiles_to_try[i];
+    for (int pair = 0; pair < 2; ++pair) {
+      if (pair && (!pair_ok || !(mt == 32 || mt == 64 || mt == 128 || mt == 256))) continue;
+      // Unless asked for, pairs are tried for the 256-token tile only (slower than one CTA below it).
+      if (pair && !pair_forced && mt != 256) continue;
+      if (!pair && pair_forced && (mt == 32 || mt == 64 || mt == 128 || mt == 256)) continue;
+      for (int mode = 0; mode < 2; ++mode) {
+        if (mode == 1 && (d->flags & HM_FLAG_NO_SPLIT_K)) continue;
+        PlanChoice c;
+        c.mt = mt;
+        c.pair = pair != 0;
+        c.mode = mode;
+        c.tiles = static_cast<int64_t>(d->shape_n / (pair ? 2 * hm::kTileN : hm::kTileN)) * ((m + mt - 1) / mt);
+        c.units = c.tiles * kb;
+        if (c.units >= (1ll << 31)) return fail(HM_ERR_INVALID, "problem too large for 32-bit unit indices");
+        if (c.tiles == 0) {
+          c.grid = 0, c.per = 0, c.cost_us = 0.0;
+        } else {
+          estimate(&c, d, kb, sms);
+        }
+        if (best.cost_us < 0.0 || c.cost_us < best.cost_us) best = c;
+      }
+    }
+  }
+  if (best.cost_us < 0.0) return fail(HM_ERR_INVALID, "no kernel for m_tile=%d with these flags", d->m_tile);
+
   memset(plan, 0, sizeof(*plan));
-  plan->m_tile = mt;
-  plan->n_tiles = d->shape_n / hm::kTileN;
-  plan->m_tiles = static_cast<int32_t>((m + mt - 1) / mt);
-  plan->kb_per_tile = d->shape_k / hm::kStageK;
-  const int64_t tiles = static_cast<int64_t>(plan->n_tiles) * plan->m_tiles;
-  const int64_t units = tiles * plan->kb_per_tile;
-  if (units >= (1ll << 31)) return fail(HM_ERR_INVALID, "problem too large for 32-bit unit indices");
-  plan->total_units = units;
+  plan->m_tile = best.mt;
+  plan->cta_pair = best.pair ? 1 : 0;
+  plan->n_tiles = d->shape_n / (best.pair ? 2 * hm::kTileN : hm::kTileN);
+  plan->m_tiles = static_cast<int32_t>((m + best.mt - 1) / best.mt);
+  plan->kb_per_tile = kb;
+  plan->total_units = best.units;
   // 8-bit activations are widened into the tail of the workspace first.
   const int64_t act16_bytes = d->a_dtype == HM_E4M3 ? ((m * d->shape_k * 2 + 255) / 256) * 256 : 0;
-  if (tiles == 0) {
+  if (best.tiles == 0) {
     plan->grid = 0;
     plan->workspace_bytes = 256;
     return HM_OK;
   }
-  // Token tiles up to 64 run two CTAs per SM (see GemmCfg::DUAL).
-  if (mt <= 64 && !(d->flags & HM_FLAG_A_OPERAND_SMEM)) sms *= 2;
-  if ((d->flags & HM_FLAG_NO_SPLIT_K) || tiles >= 4ll * sms) {
-    plan->mode = 0;
-    plan->grid = static_cast<int32_t>(tiles < sms ? tiles : sms);
-    plan->units_per_cta = 0;
+  const int64_t per_worker = best.pair ? 2 : 1;  // 128-row tiles (counters, partial slots) per scheduled tile / worker
+  plan->mode = best.mode;
+  plan->grid = static_cast<int32_t>(best.grid);
+  plan->units_per_cta = static_cast<int32_t>(best.per);
+  if (best.mode == 0) {
     plan->workspace_bytes = 256 + act16_bytes;
   } else {
-    plan->mode = 1;
-    const int64_t min_units = 2;  // do not cut work finer than two 128-K steps per CTA
-    int64_t max_ctas = units / min_units;
-    if (max_ctas < 1) max_ctas = 1;
-    int64_t grid = max_ctas < sms ? max_ctas : sms;
-    const int64_t per = (units + grid - 1) / grid;
-    grid = (units + per - 1) / per;
-    plan->grid = static_cast<int32_t>(grid);
-    plan->units_per_cta = static_cast<int32_t>(per);
-    int64_t counters = ((tiles * 4 * 4 + 255) / 256) * 256;
-    plan->workspace_bytes = 256 + counters + grid * 2 * static_cast<int64_t>(mt) * hm::kTileN * 4 + act16_bytes;
+    const int64_t counters = ((best.tiles * per_worker * 4 * 4 + 255) / 256) * 256;
+    plan->workspace_bytes = 256 + counters + best.grid * per_worker * 2 * static_cast<int64_t>(best.mt) * hm::kTileN * 4 + act16_bytes;
   }
   return HM_OK;
 }
@@ -181,6 +275,42 @@ int launch_gemm(const hm::GemmParams& p, const CUtensorMap& tmap, int grid, cuda
   kern<<<grid, Cfg::THREADS, Cfg::SMEM_ALLOC, stream>>>(p, tmap);
   HM_CUDA_OK(cudaGetLastError());
   return HM_OK;
+}
+
+// CTA-pair kernel: `pairs` clusters of two CTAs.
+template <int MT, bool BF16, bool HAS_ZP>
+int launch_gemm_pair(const hm::GemmParams& p, const CUtensorMap& tmap, int pairs, cudaStream_t stream) {
+  using Cfg = hm::GemmCfg<MT, true, true>;
+  auto kern = hm::gemm_w4a16_kernel<MT, BF16, HAS_ZP, true, false, 0, true>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  HM_CUDA_OK(cudaGetDevice(&dev));
+  if (!configured[dev & 63]) {
+    HM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_ALLOC));
+    HM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+    configured[dev & 63] = true;
+  }
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs), 1, 1);
+  cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_ALLOC;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  HM_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p, tmap));
+  return HM_OK;
+}
+
+template <int MT>
+int dispatch_gemm_pair(bool bf16, bool zp, const hm::GemmParams& p, const CUtensorMap& tmap, int pairs, cudaStream_t stream) {
+  if (bf16) return zp ? launch_gemm_pair<MT, true, true>(p, tmap, pairs, stream) : launch_gemm_pair<MT, true, false>(p, tmap, pairs, stream);
+  return zp ? launch_gemm_pair<MT, false, true>(p, tmap, pairs, stream) : launch_gemm_pair<MT, false, false>(p, tmap, pairs, stream);
 }
 
 template <int MT>
@@ -413,7 +543,8 @@ int hm_gemm(const hm_gemm_desc* desc, int64_t m, const void* a, int64_t lda, con
   }
   const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(desc->shape_k), static_cast<cuuint64_t>(m)};
   const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(lda) * 2};
-  const cuuint32_t box[2] = {static_cast<cuuint32_t>(hm::kBlockK), static_cast<cuuint32_t>(pl.m_tile)};
+  // In a CTA pair each CTA loads half of the token tile's rows.
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(hm::kBlockK), static_cast<cuuint32_t>(pl.cta_pair ? pl.m_tile / 2 : pl.m_tile)};
   const cuuint32_t estr[2] = {1, 1};
   CUresult cr = encode(&tmap, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
                        const_cast<void*>(a), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -431,7 +562,7 @@ int hm_gemm(const hm_gemm_desc* desc, int64_t m, const void* a, int64_t lda, con
   auto ws = static_cast<uint8_t*>(workspace);
   p.status = reinterpret_cast<int*>(ws);
   p.counters = reinterpret_cast<int*>(ws + 256);
-  const int64_t tiles = static_cast<int64_t>(pl.n_tiles) * pl.m_tiles;
+  const int64_t tiles = static_cast<int64_t>(pl.n_tiles) * pl.m_tiles * (pl.cta_pair ? 2 : 1);
   const int64_t counters = ((tiles * 4 * 4 + 255) / 256) * 256;
   p.partials = reinterpret_cast<float*>(ws + 256 + (pl.mode == 1 ? counters : 0));
   p.M = static_cast<int>(m);
@@ -448,6 +579,15 @@ int hm_gemm(const hm_gemm_desc* desc, int64_t m, const void* a, int64_t lda, con
 
   const bool a_tmem = !(desc->flags & HM_FLAG_A_OPERAND_SMEM);
   auto s = static_cast<cudaStream_t>(stream);
+  if (pl.cta_pair) {
+    switch (pl.m_tile) {
+      case 32: return dispatch_gemm_pair<32>(bf16, desc->has_zp != 0, p, tmap, pl.grid, s);
+      case 64: return dispatch_gemm_pair<64>(bf16, desc->has_zp != 0, p, tmap, pl.grid, s);
+      case 128: return dispatch_gemm_pair<128>(bf16, desc->has_zp != 0, p, tmap, pl.grid, s);
+      case 256: return dispatch_gemm_pair<256>(bf16, desc->has_zp != 0, p, tmap, pl.grid, s);
+    }
+    return fail(HM_ERR_INVALID, "no CTA-pair kernel for m_tile=%d", pl.m_tile);
+  }
   switch (pl.m_tile) {
     case 16: return dispatch_gemm<16>(bf16, desc->has_zp != 0, a_tmem, wfmt, p, tmap, pl.grid, s);
     case 32: return dispatch_gemm<32>(bf16, desc->has_zp != 0, a_tmem, wfmt, p, tmap, pl.grid, s);

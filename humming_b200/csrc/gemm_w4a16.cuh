@@ -91,10 +91,14 @@ struct GemmParams {
   const float* act_scale;      // per activation row fp32 scale, multiplied into the output, or null
 };
 
-template <int MT, bool A_TMEM>
+// PAIR: two CTAs (a cluster of 2) compute 256 weight rows x MT tokens with
+// cta_group::2 MMAs issued by the leader; each CTA dequantizes its own 128
+// rows into its own tensor memory and loads only half of the activation rows.
+template <int MT, bool A_TMEM, bool PAIR = false>
 struct GemmCfg {
   static_assert(MT == 16 || MT == 32 || MT == 64 || MT == 128 || MT == 192 || MT == 256, "token tile");
   static_assert(A_TMEM || MT <= 128, "the shared-memory operand variant is built for tiles up to 128 tokens");
+  static_assert(!PAIR || (A_TMEM && MT % 32 == 0), "cta_group::2 needs the TMEM operand and a token tile that is a multiple of 32");
   // Ring depths, all in 128-K stages: SA operand slots for the dequantized
   // weights (64 TMEM columns, or 32 KB of shared memory in the cross-check
   // variant), SX activation stages (two 64-K boxes each, shared memory), SW
@@ -103,12 +107,16 @@ struct GemmCfg {
   // one MMA-issuing thread (>= 45-52 cycles per K=16 MMA whatever N is), not by
   // the tensor pipe: two CTAs share an SM there (half the tensor memory, half
   // the warps and ring slots each) so that two issue streams interleave.
-  static constexpr bool DUAL = A_TMEM && MT <= 64;
+  static constexpr bool DUAL = A_TMEM && MT <= 64 && !PAIR;
   static constexpr int CTAS_PER_SM = DUAL ? 2 : 1;
   static constexpr int SA = (!A_TMEM || MT == 192 || DUAL) ? 2 : 4;
-  // An activation stage is released by the same tcgen05.commit as the operand
-  // slot of its step (one commit per step), so its ring cannot be deeper.
-  static constexpr int SX = MT <= 128 ? SA : 2;
+  // An activation stage is normally released by the same tcgen05.commit as the
+  // operand slot of its step (one commit per step), so its ring cannot be deeper
+  // than SA.  With two CTAs per SM only two operand slots fit, which is too
+  // shallow to hide the latency of the activation loads (about 1300 cycles
+  // against steps of 800): there the ring gets barriers and a commit of its own.
+  static constexpr bool X_OWN_RING = DUAL;
+  static constexpr int SX = X_OWN_RING ? (MT <= 32 ? 8 : 4) : ((MT <= 128 || PAIR) ? SA : 2);
   static constexpr int SW = DUAL ? 4 : (MT <= 64 ? 8 : 4);
   // Dequant warp groups (4 warps each) taking stages round-robin.  A slot (and a
   // weight stage) must always be refilled by the group that filled it before:
@@ -124,7 +132,8 @@ struct GemmCfg {
   static constexpr int A_COL0 = ACC_BUFS * MT;
   static constexpr int USED_COLS = A_COL0 + (A_TMEM ? SA * A_SLOT_COLS : 0);
   static constexpr int TMEM_COLS = USED_COLS <= 32 ? 32 : USED_COLS <= 64 ? 64 : USED_COLS <= 128 ? 128 : USED_COLS <= 256 ? 256 : 512;
-  static constexpr int X_BOX = MT * 128;                   // one 64-K box
+  static constexpr int X_ROWS = PAIR ? MT / 2 : MT;        // activation rows this CTA loads
+  static constexpr int X_BOX = X_ROWS * 128;               // one 64-K box
   static constexpr int X_STAGE = 2 * X_BOX;
   static constexpr int A_HALF = kTileN * 128;              // one 64-K half of a shared-memory operand slot
   static constexpr int A_STAGE = A_TMEM ? 0 : 2 * A_HALF;
@@ -133,13 +142,20 @@ struct GemmCfg {
   static constexpr int SMEM_W = SMEM_A + SA * A_STAGE;
   static constexpr int SMEM_STAGE = SMEM_W + SW * kWStageBytes;  // epilogue transpose staging, 2 KB per warp
   static constexpr int SMEM_BAR = SMEM_STAGE + 4 * 2048 + 1024;  // + gathered-row indices of the MoE producer
-  static constexpr int SMEM_TOTAL = SMEM_BAR + kNumBarrierSlots * 8 + 64;
+  static constexpr int SMEM_TOTAL = SMEM_BAR + kNumBarrierSlots * 8 + 256;  // + TMEM address, abort flags, pending reductions
   static constexpr int SMEM_ALLOC = SMEM_TOTAL + 1024;  // slack for manual 1024-byte alignment
   static_assert(USED_COLS <= 512, "tensor memory budget");
   static_assert(SMEM_ALLOC <= 232448, "shared memory budget");
-  static_assert(2 * SW + SX + 2 * SA + 5 <= kNumBarrierSlots, "barrier slots");
+  static_assert(!DUAL || SMEM_ALLOC <= 115712, "two CTAs per SM: half of the shared memory each");
+  static_assert(2 * SW + 2 * SX + 2 * SA + 5 <= kNumBarrierSlots, "barrier slots");
   static_assert(SA % NGROUPS == 0 && SW % NGROUPS == 0, "each ring slot belongs to one dequant group");
-  static_assert(SX <= SA, "activation stages are released through the operand-slot barriers");
+  static_assert(X_OWN_RING || SX <= SA, "activation stages are released through the operand-slot barriers");
+};
+
+// A partial tile whose contributors have all published: see the reduction at the end of the kernel.
+struct PendingReduce {
+  int tile, m_tile, n_tile, nseg, first_cta, m_valid;
+  int last[4];  // per 32-row quarter: this CTA was the last contributor to arrive
 };
 
 template <bool BF16>
@@ -195,10 +211,12 @@ struct Ring {
 // device.
 // WFMT: 0 = 4-bit integer codes with 16-bit group scales (+ zero points);
 //       1 = FP4 e2m1 codes with UE8M0 scales per 32 K-elements (MXFP4), bf16 compute.
-template <int MT, bool BF16, bool HAS_ZP, bool A_TMEM, bool MOE = false, int WFMT = 0>
-__global__ void __launch_bounds__(GemmCfg<MT, A_TMEM>::THREADS, GemmCfg<MT, A_TMEM>::CTAS_PER_SM)
+template <int MT, bool BF16, bool HAS_ZP, bool A_TMEM, bool MOE = false, int WFMT = 0, bool PAIR = false>
+__global__ void __launch_bounds__(GemmCfg<MT, A_TMEM, PAIR>::THREADS, GemmCfg<MT, A_TMEM, PAIR>::CTAS_PER_SM)
 gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
-  using Cfg = GemmCfg<MT, A_TMEM>;
+  using Cfg = GemmCfg<MT, A_TMEM, PAIR>;
+  static_assert(!PAIR || !MOE, "the MoE GEMM has no CTA-pair variant");
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;  // 0 = leader of the pair
   constexpr int SX = Cfg::SX;
   constexpr int SA = Cfg::SA;
   constexpr int SW = Cfg::SW;
@@ -221,12 +239,16 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
   // a_empty(slot): the MMAs of the step that used operand slot `slot` (and the
   // activation stage of that step) have completed.
   auto a_empty = [&](int i) { return bar0 + 8u * (2 * SW + SX + SA + i); };
-  constexpr int kBarAcc = 2 * SW + SX + 2 * SA;
+  auto x_empty = [&](int i) { return bar0 + 8u * (2 * SW + SX + 2 * SA + i); };  // X_OWN_RING only
+  constexpr int kBarAcc = 2 * SW + 2 * SX + 2 * SA;
   auto acc_full = [&](int i) { return bar0 + 8u * (kBarAcc + i); };
   auto acc_empty = [&](int i) { return bar0 + 8u * (kBarAcc + 2 + i); };
   const uint32_t drain_bar = bar0 + 8u * (kBarAcc + 4);
   volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem_gen + Cfg::SMEM_BAR + kNumBarrierSlots * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + Cfg::SMEM_BAR + kNumBarrierSlots * 8 + 8);
+  // Up to two partial tiles per CTA (the first and the last of its run) whose sum over the contributors
+  // falls to this CTA; filled by the epilogue warps, worked off by all warps at the end.
+  PendingReduce* pending = reinterpret_cast<PendingReduce*>(smem_gen + Cfg::SMEM_BAR + kNumBarrierSlots * 8 + 32);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -236,28 +258,39 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
       mbar_init(w_full(i), 2);  // code producer + scale/zero-point producer
       mbar_init(w_empty(i), 4);
     }
-    for (int i = 0; i < SX; ++i) mbar_init(x_full(i), 1);
+    for (int i = 0; i < SX; ++i) {
+      mbar_init(x_full(i), 1);
+      mbar_init(x_empty(i), 1);
+    }
     for (int i = 0; i < SA; ++i) {
-      mbar_init(a_full(i), 4);
+      mbar_init(a_full(i), PAIR ? 8 : 4);  // pair: both CTAs' dequant warps arrive on the leader's barrier
       mbar_init(a_empty(i), 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(acc_full(i), 1);
-      mbar_init(acc_empty(i), 4);
+      mbar_init(acc_empty(i), PAIR ? 8 : 4);
     }
     mbar_init(drain_bar, 1);
+    for (int e = 0; e < 2; ++e)
+      for (int qq = 0; qq < 4; ++qq) pending[e].last[qq] = 0;
     abort_flag[0] = 0;  // raised by the first wait that gives up
     abort_flag[1] = 0;  // separate flag for the drain waits of the abort path
     mbar_fence_init();
     fence_proxy_async_smem();
   }
   if (warp == 3) {
-    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_holder)), Cfg::TMEM_COLS);
-    tmem_relinquish();
+    if constexpr (PAIR) {
+      tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_holder)), Cfg::TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_holder)), Cfg::TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   if (!MOE && warp == 1 && lane == 0) tma_prefetch_desc(&tmap_x);
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();  // the peer's barriers are initialised before anyone signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
@@ -274,11 +307,14 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
     sched.units_per_cta = per;
   }
   SegIter iter;
-  iter.init(sched, blockIdx.x);
+  iter.init(sched, PAIR ? (blockIdx.x >> 1) : blockIdx.x);  // a pair shares one schedule slot
   Segment seg;
+  // 128-row weight tile this CTA works on: a pair's tile covers two of them.
+  auto ntile = [&](const Segment& s) -> int { return PAIR ? s.n_tile * 2 + static_cast<int>(rank) : s.n_tile; };
+  const int n_tiles_128 = PAIR ? sched.n_tiles * 2 : sched.n_tiles;
   // Per-expert strides of the prepared buffers (MoE only).
-  const size_t expert_code_bytes = static_cast<size_t>(sched.n_tiles) * sched.kb_per_tile * (2 * kCodeBytes);
-  const size_t expert_groups = static_cast<size_t>(sched.n_tiles) * p.groups;
+  const size_t expert_code_bytes = static_cast<size_t>(n_tiles_128) * sched.kb_per_tile * (2 * kCodeBytes);
+  const size_t expert_groups = static_cast<size_t>(n_tiles_128) * p.groups;
   auto expert_of = [&](const Segment& s) -> size_t { return MOE ? static_cast<size_t>(p.expert_ids[s.m_tile]) : 0; };
   const bool tracing = p.trace != nullptr && blockIdx.x == 0;
   auto trace = [&](int role, int idx, int j) {
@@ -286,6 +322,8 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
   };
 
   if (threadIdx.x == 0) trace(7, 0, 0);
+  // Tracing only: wall-clock entry / exit time of every CTA (first 1024), after the role timeline.
+  if (p.trace != nullptr && threadIdx.x == 0 && blockIdx.x < 1024) p.trace[8 * kTraceEvents * 4 + blockIdx.x * 2] = globaltimer_ns();
   if (warp == 0) {
     // ------------------------------------------------ weight producer (packed codes)
     if (lane == 0) {
@@ -294,7 +332,7 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
       int it = 0;
       bool ok = true;
       while (ok && iter.next(seg)) {
-        const uint8_t* codes = p.w + (static_cast<size_t>(seg.n_tile) * sched.kb_per_tile + seg.kb0) * (2 * kCodeBytes) +
+        const uint8_t* codes = p.w + (static_cast<size_t>(ntile(seg)) * sched.kb_per_tile + seg.kb0) * (2 * kCodeBytes) +
                                expert_of(seg) * expert_code_bytes;
         for (int ks = seg.kb0; ks < seg.kb1; ++ks, ++it) {
           if (!mbar_wait_bounded(w_empty(ring.idx), ring.phase ^ 1, abort_flag)) {
@@ -346,7 +384,7 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
           g = seg.kb0 / p.steps_per_group;
           cnt = seg.kb0 - g * p.steps_per_group;
         }
-        const size_t grp0 = expert_of(seg) * expert_groups + static_cast<size_t>(seg.n_tile) * p.groups + g;
+        const size_t grp0 = expert_of(seg) * expert_groups + static_cast<size_t>(ntile(seg)) * p.groups + g;
         const uint8_t* scales = WFMT == 1 ? p.w_scale + (grp0 + 4 * static_cast<size_t>(seg.kb0)) * kTileN
                                           : p.w_scale + grp0 * kScaleBytes;
         const uint8_t* zps = HAS_ZP ? p.w_zp + grp0 * kZpBytes : nullptr;
@@ -391,11 +429,13 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
     // 16-byte chunk c of row r lands at chunk (c ^ (r & 7)) of its 128-byte line,
     // 8-row groups 1024 bytes apart -- the layout of a 128-byte-swizzled TMA box.
     // Copies of a stage form one cp.async group; a stage is published (proxy
-    // fence + arrive) once its group has landed, SX-1 stages later.
+    // fence + arrive) once its group has landed, XLAG stages later (half the ring,
+    // so that the issuer of new copies stays ahead of the MMAs by the other half).
+    constexpr int XLAG = SX > 2 ? SX / 2 : SX - 1;
     int* xrow = reinterpret_cast<int*>(smem_gen + Cfg::SMEM_STAGE + 4 * 2048);  // source row per token of the tile
     Ring<SX> ring;      // stage being filled
     Ring<SX> publish;   // oldest stage not yet published
-    Ring<SA> done;
+    Ring<Cfg::X_OWN_RING ? SX : SA> done;  // barrier whose completion frees stage ring.idx (step it - SX)
     int it = 0, published = 0;
     bool ok = true;
     const int sub_row = lane >> 3, chunk = lane & 7;
@@ -409,7 +449,7 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
       int col = seg.kb0 * kStageK;
       for (int ks = seg.kb0; ks < seg.kb1; ++ks, ++it) {
         if (it >= SX) {
-          if (!mbar_wait_bounded(a_empty(done.idx), done.phase, abort_flag)) {
+          if (!mbar_wait_bounded(Cfg::X_OWN_RING ? x_empty(done.idx) : a_empty(done.idx), done.phase, abort_flag)) {
             if (lane == 0) report_abort(p.status, HM_ABORT_X_EMPTY, it, ring.idx);
             ok = false;
             break;
@@ -432,8 +472,8 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
         cp_async_commit();
         col += kStageK;
         ring.advance();
-        if (it - published >= SX - 1) {
-          cp_async_wait<SX - 1>();
+        if (it - published >= XLAG) {
+          cp_async_wait<XLAG>();
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) mbar_arrive(x_full(publish.idx));
@@ -455,15 +495,15 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
     // ------------------------------------------------ activation producer
     if (lane == 0) {
       Ring<SX> ring;
-      Ring<SA> done;  // operand-slot barrier of step (it - SX), whose completion frees stage ring.idx
+      Ring<Cfg::X_OWN_RING ? SX : SA> done;  // barrier of step (it - SX), whose completion frees stage ring.idx
       int it = 0;
       bool ok = true;
       while (ok && iter.next(seg)) {
-        const int row0 = seg.m_tile * MT;
+        const int row0 = seg.m_tile * MT + (PAIR ? static_cast<int>(rank) * Cfg::X_ROWS : 0);
         int col = seg.kb0 * kStageK;
         for (int ks = seg.kb0; ks < seg.kb1; ++ks, ++it) {
           if (it >= SX) {
-            if (!mbar_wait_bounded(a_empty(done.idx), done.phase, abort_flag)) {
+            if (!mbar_wait_bounded(Cfg::X_OWN_RING ? x_empty(done.idx) : a_empty(done.idx), done.phase, abort_flag)) {
               report_abort(p.status, HM_ABORT_X_EMPTY, it, ring.idx);
               ok = false;
               break;
@@ -472,10 +512,15 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
           }
           trace(1, it, 0);
           const uint32_t bar = x_full(ring.idx);
-          if (p.dbg & HM_DBG_SKIP_X_LOAD) {
+          const uint32_t dst = x_smem + ring.idx * Cfg::X_STAGE;
+          if constexpr (PAIR) {
+            // Both CTAs' halves are counted on the leader's barrier; the leader arms it for both.
+            if (rank == 0) mbar_arrive_expect_tx(bar, 2 * Cfg::X_STAGE);
+            tma_load_2d_pair(dst, &tmap_x, col, row0, leader_smem_addr(bar));
+            tma_load_2d_pair(dst + Cfg::X_BOX, &tmap_x, col + kBlockK, row0, leader_smem_addr(bar));
+          } else if (p.dbg & HM_DBG_SKIP_X_LOAD) {
             mbar_arrive(bar);
           } else {
-            const uint32_t dst = x_smem + ring.idx * Cfg::X_STAGE;
             mbar_arrive_expect_tx(bar, Cfg::X_STAGE);
             tma_load_2d(dst, &tmap_x, col, row0, bar);
             tma_load_2d(dst + Cfg::X_BOX, &tmap_x, col + kBlockK, row0, bar);
@@ -485,7 +530,7 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
           ring.advance();
         }
       }
-      if (!ok) {
+      if (!ok && rank == 0) {
         for (int j = 0; j < SX && j < it; ++j) {
           const int last_it = it - 1 - j;
           mbar_wait_bounded(x_full(last_it % SX), (last_it / SX) & 1, abort_flag + 1);
@@ -493,9 +538,12 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
       }
     }
   } else if (warp == 2) {
-    // ------------------------------------------------ MMA issuer (one thread)
-    if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc(BF16 ? 1 : 0, BF16 ? 1 : 0, kTileN, MT);
+    // ------------------------------------------------ MMA issuer (one thread; in a pair only the leader's)
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = umma_idesc(BF16 ? 1 : 0, BF16 ? 1 : 0, PAIR ? 2 * kTileN : kTileN, MT);
+      auto wait_op = [&](uint32_t bar, uint32_t parity) {
+        return PAIR ? mbar_wait_bounded_cluster(bar, parity, abort_flag) : mbar_wait_bounded(bar, parity, abort_flag);
+      };
       const uint64_t desc_hi = umma_desc_sw128(0) & 0xFFFFFFFF00000000ull;
       const uint32_t desc_lo_const = static_cast<uint32_t>(umma_desc_sw128(0)) & 0xFFFFC000u;
       Ring<SA> ra;
@@ -507,7 +555,7 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
       while (ok && iter.next(seg)) {
         const int b = sc % ACC_BUFS;
         const uint32_t acc_ph = (sc / ACC_BUFS) & 1;
-        if (!mbar_wait_bounded(acc_empty(b), acc_ph ^ 1, abort_flag)) {
+        if (!wait_op(acc_empty(b), acc_ph ^ 1)) {
           report_abort(p.status, HM_ABORT_MMA_ACC, sc, b);
           ok = false;
           break;
@@ -516,8 +564,7 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
         for (int ks = seg.kb0; ks < seg.kb1; ++ks, ++it) {
           trace(2, it, 0);
           if (!ready) {
-            if (!mbar_wait_bounded(a_full(ra.idx), ra.phase, abort_flag) ||
-                !mbar_wait_bounded(x_full(rx.idx), rx.phase, abort_flag)) {
+            if (!wait_op(a_full(ra.idx), ra.phase) || !wait_op(x_full(rx.idx), rx.phase)) {
               report_abort(p.status, HM_ABORT_MMA_OPERANDS, it, ra.idx);
               ok = false;
               break;
@@ -526,11 +573,16 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
           trace(2, it, 1);
           tc_fence_after();
           const uint32_t slot = ra.idx;
-          const uint32_t b_lo0 = desc_lo_const | ((x_smem + rx.idx * Cfg::X_STAGE) >> 4);
+          const uint32_t xs = rx.idx;
+          const uint32_t b_lo0 = desc_lo_const | ((x_smem + xs * Cfg::X_STAGE) >> 4);
           ra.advance();
           rx.advance();
           const uint32_t acc0 = ks != seg.kb0 ? 1u : 0u;
-          if constexpr (A_TMEM) {
+          if constexpr (PAIR) {
+            ready = mma_step_f16_ts_pair(d_tmem, tmem_base + Cfg::A_COL0 + slot * Cfg::A_SLOT_COLS, desc_hi | b_lo0,
+                                         Cfg::X_BOX >> 4, idesc, acc0, a_empty(slot), a_full(ra.idx), ra.phase,
+                                         x_full(rx.idx), rx.phase, (p.dbg & HM_DBG_SKIP_MMA) != 0);
+          } else if constexpr (A_TMEM) {
             // MMAs + commit + look-ahead probe of the next step's barriers in one block.
             ready = mma_step_f16_ts(d_tmem, tmem_base + Cfg::A_COL0 + slot * Cfg::A_SLOT_COLS, desc_hi | b_lo0,
                                     Cfg::X_BOX >> 4, idesc, acc0, a_empty(slot), a_full(ra.idx), ra.phase,
@@ -548,15 +600,16 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
             tc_commit(a_empty(slot));
             ready = false;
           }
+          if constexpr (Cfg::X_OWN_RING) tc_commit(x_empty(xs));
           trace(2, it, 3);
         }
         if (!ok) break;
-        tc_commit(acc_full(b));
+        if constexpr (PAIR) tc_commit_pair(acc_full(b)); else tc_commit(acc_full(b));
         ++sc;
       }
       if (!ok) {
         // Abort path: wait for MMAs already issued before TMEM is released.
-        tc_commit(drain_bar);
+        if constexpr (PAIR) tc_commit_pair(drain_bar); else tc_commit(drain_bar);
         mbar_wait_bounded(drain_bar, 0, abort_flag + 1);
       }
     }
@@ -660,7 +713,9 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
           fence_proxy_async_smem();
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(a_full(s));
+        if (lane == 0) {
+          if (PAIR && rank != 0) mbar_arrive_cluster(a_full(s), 0); else mbar_arrive(a_full(s));
+        }
         if (q == 0 && lane == 0) trace(3 + group, it, 3);
         rw.advance_by(NGROUPS);
         ra.advance_by(NGROUPS);
@@ -671,6 +726,7 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
     const int q = warp & 3;
     const int row = q * 32 + lane;
     int sc = 0;
+    int npartial = 0;  // partial tiles seen so far (at most two per CTA)
     bool ok = true;
     while (ok && iter.next(seg)) {
       const int b = sc % ACC_BUFS;
@@ -681,11 +737,13 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
       }
       tc_fence_after();
       if (q == 0 && lane == 0) trace(7, sc + 1, 0);
-      const int n = seg.n_tile * kTileN + row;
+      const int n = ntile(seg) * kTileN + row;
       const int m0 = seg.m_tile * MT;
       const int m_valid = MOE ? MT : ((p.M - m0) < MT ? (p.M - m0) : MT);
       const float bias = (p.bias != nullptr) ? load_bias<BF16>(p.bias, static_cast<int>(expert_of(seg)) * p.N + n) : 0.f;
-      float* slot = p.partials + static_cast<size_t>(seg.slot) * (MT * kTileN);
+      // Partial-tile slots and counters are per 128-row tile: a pair uses two of each.
+      const int slot_mul = PAIR ? 2 : 1;
+      float* slot = p.partials + static_cast<size_t>(seg.slot * slot_mul + rank) * (MT * kTileN);
       const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + b * MT;
       constexpr int CH = MT >= 32 ? 32 : 16;  // token columns per chunk
       uint8_t* stage = smem_gen + Cfg::SMEM_STAGE + q * 2048;  // this warp's [CH tokens][32 rows] 16-bit tile
@@ -730,7 +788,7 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
             }
           }
           __syncwarp();
-          const int n_base = seg.n_tile * kTileN + q * 32;
+          const int n_base = ntile(seg) * kTileN + q * 32;
 #pragma unroll
           for (int i = 0; i < CH / 8; ++i) {
             const int j = i * 8 + (lane >> 2);
@@ -756,7 +814,9 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
       // Accumulator drained: the MMA issuer may overwrite it.
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(acc_empty(b));
+      if (lane == 0) {
+        if (PAIR && rank != 0) mbar_arrive_cluster(acc_empty(b), 0); else mbar_arrive(acc_empty(b));
+      }
       if (q == 0 && lane == 0) trace(7, sc + 1, 1);
       ++sc;
 
@@ -767,51 +827,25 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
         __syncwarp();
         int last = 0;
         if (lane == 0) {
-          int* ctr = p.counters + seg.tile * 4 + q;
+          int* ctr = p.counters + (seg.tile * slot_mul + rank) * 4 + q;
           const int old = atomicAdd(ctr, 1);
           last = (old == seg.nseg - 1) ? 1 : 0;
           if (last) *ctr = 0;  // leave the workspace clean for the next launch
         }
-        last = __shfl_sync(0xffffffffu, last, 0);
-        if (last) {
-          __threadfence();
-          // Sum the contributors in CTA order (a fixed order, so the result does
-          // not depend on who arrived last); 8 columns at a time keeps 8 loads per
-          // contributor in flight.
-          for (int j0 = 0; j0 < m_valid; j0 += 8) {
-            float acc[8];
-#pragma unroll
-            for (int jj = 0; jj < 8; ++jj) acc[jj] = 0.f;
-            for (int cs = 0; cs < seg.nseg; ++cs) {
-              const int cta = seg.first_cta + cs;
-              const float* src = p.partials + static_cast<size_t>(sched_slot(sched, cta, seg.tile)) * (MT * kTileN) +
-                                 j0 * kTileN + row;
-              float v[8];
-#pragma unroll
-              for (int jj = 0; jj < 8; ++jj) v[jj] = (j0 + jj < m_valid) ? __ldcg(src + jj * kTileN) : 0.f;
-#pragma unroll
-              for (int jj = 0; jj < 8; ++jj) acc[jj] += v[jj];
-            }
-#pragma unroll
-            for (int jj = 0; jj < 8; ++jj) {
-              if (j0 + jj < m_valid) {
-                int out_row = m0 + j0 + jj;
-                float o = acc[jj];
-                if constexpr (MOE) {
-                  out_row = p.sorted_ids[m0 + j0 + jj];
-                  if (out_row >= p.num_valid) continue;
-                  if (p.act_scale != nullptr) o *= p.act_scale[p.is_down ? out_row : out_row / p.top_k];
-                  o += bias;
-                  if (p.is_down) o *= p.topk_weights[out_row];
-                } else {
-                  if (p.act_scale != nullptr) o *= p.act_scale[out_row];
-                  o += bias;
-                }
-                store_out<BF16>(p.c, static_cast<size_t>(out_row) * p.ldc + n, o);
-              }
-            }
+        if (lane == 0 && npartial < 2) {
+          PendingReduce& rec = pending[npartial];
+          if (q == 0) {
+            rec.tile = seg.tile;
+            rec.m_tile = seg.m_tile;
+            rec.n_tile = seg.n_tile;
+            rec.nseg = seg.nseg;
+            rec.first_cta = seg.first_cta;
+            rec.m_valid = m_valid;
           }
+          rec.last[q] = last;
+          if (last) __threadfence();
         }
+        ++npartial;
       }
     }
   }
@@ -819,10 +853,92 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
   // Every role ends here, also after an abort (all waits are bounded).
   tc_fence_before();
   __syncthreads();
+
+  // ------------------------------------------------ sums of the partial tiles this CTA arrived last at
+  // All warps take part: work items are (4 tokens x 32 weight rows), a lane holds 4
+  // consecutive rows of one token, and the loads of up to RC contributors are in
+  // flight at once.  The contributors are added in CTA order, so the result does
+  // not depend on which CTA arrived last.
+  if (*abort_flag == 0) {
+    constexpr int RC = Cfg::CTAS_PER_SM == 2 ? 4 : 8;
+    constexpr int slot_mul = PAIR ? 2 : 1;
+    const int r4 = (lane & 7) * 4;
+    const int tsub = lane >> 3;
+    for (int e = 0; e < 2; ++e) {
+      const PendingReduce& rec = pending[e];
+      if ((rec.last[0] | rec.last[1] | rec.last[2] | rec.last[3]) == 0) continue;
+      const int n_tile128 = PAIR ? rec.n_tile * 2 + static_cast<int>(rank) : rec.n_tile;
+      const int expert = MOE ? p.expert_ids[rec.m_tile] : 0;
+      const int m0 = rec.m_tile * MT;
+      const int items = ((rec.m_valid + 3) >> 2) * 4;
+      for (int item = warp; item < items; item += Cfg::THREADS / 32) {
+        const int q = item & 3;
+        if (!rec.last[q]) continue;
+        const int tok = (item >> 2) * 4 + tsub;
+        const bool in = tok < rec.m_valid;
+        const int n4 = n_tile128 * kTileN + q * 32 + r4;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int cs0 = 0; cs0 < rec.nseg; cs0 += RC) {
+          float4 v[RC];
+#pragma unroll
+          for (int c = 0; c < RC; ++c) {
+            const int cs = cs0 + c;
+            v[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (in && cs < rec.nseg) {
+              const float* src = p.partials +
+                                 static_cast<size_t>(sched_slot(sched, rec.first_cta + cs, rec.tile) * slot_mul + rank) * (MT * kTileN) +
+                                 tok * kTileN + q * 32 + r4;
+              v[c] = __ldcg(reinterpret_cast<const float4*>(src));
+            }
+          }
+#pragma unroll
+          for (int c = 0; c < RC; ++c) {
+            acc.x += v[c].x;
+            acc.y += v[c].y;
+            acc.z += v[c].z;
+            acc.w += v[c].w;
+          }
+        }
+        if (!in) continue;
+        int out_row = m0 + tok;
+        float sc_tok = 1.f, w_tok = 1.f;
+        if constexpr (MOE) {
+          out_row = p.sorted_ids[m0 + tok];
+          if (out_row >= p.num_valid) continue;
+          if (p.act_scale != nullptr) sc_tok = p.act_scale[p.is_down ? out_row : out_row / p.top_k];
+          if (p.is_down) w_tok = p.topk_weights[out_row];
+        } else {
+          if (p.act_scale != nullptr) sc_tok = p.act_scale[out_row];
+        }
+        float b4[4] = {0.f, 0.f, 0.f, 0.f};
+        if (p.bias != nullptr) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) b4[i] = load_bias<BF16>(p.bias, expert * p.N + n4 + i);
+        }
+        const float o0 = (acc.x * sc_tok + b4[0]) * w_tok;
+        const float o1 = (acc.y * sc_tok + b4[1]) * w_tok;
+        const float o2 = (acc.z * sc_tok + b4[2]) * w_tok;
+        const float o3 = (acc.w * sc_tok + b4[3]) * w_tok;
+        uint2 packed;
+        if constexpr (BF16) {
+          __nv_bfloat162 lo = __floats2bfloat162_rn(o0, o1), hi = __floats2bfloat162_rn(o2, o3);
+          packed.x = *reinterpret_cast<uint32_t*>(&lo);
+          packed.y = *reinterpret_cast<uint32_t*>(&hi);
+        } else {
+          __half2 lo = __floats2half2_rn(o0, o1), hi = __floats2half2_rn(o2, o3);
+          packed.x = *reinterpret_cast<uint32_t*>(&lo);
+          packed.y = *reinterpret_cast<uint32_t*>(&hi);
+        }
+        *reinterpret_cast<uint2*>(static_cast<uint8_t*>(p.c) + (static_cast<size_t>(out_row) * p.ldc + n4) * 2) = packed;
+      }
+    }
+  }
+  if constexpr (PAIR) cluster_sync_all();  // no CTA leaves while its peer may still signal it or read its memory
   if (threadIdx.x == 0) trace(7, 0, 3);
+  if (p.trace != nullptr && threadIdx.x == 0 && blockIdx.x < 1024) p.trace[8 * kTraceEvents * 4 + blockIdx.x * 2 + 1] = globaltimer_ns();
   if (warp == 3) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    if constexpr (PAIR) tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS); else tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
 }
 

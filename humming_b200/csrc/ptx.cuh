@@ -97,6 +97,57 @@ HM_DEVICE bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* ab
   }
 }
 
+// ---------------------------------------------------------------- CTA pairs (cluster of 2)
+HM_DEVICE uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// All threads of both CTAs.
+HM_DEVICE void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrive on the barrier at the same shared-memory offset in CTA `cta` of the cluster.
+HM_DEVICE void mbar_arrive_cluster(uint32_t bar, uint32_t cta) {
+  asm volatile(
+      "{\n\t.reg .b32 ra;\n\t"
+      "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
+      "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n\t}" ::"r"(bar),
+      "r"(cta)
+      : "memory");
+}
+HM_DEVICE bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait with cluster-scope acquire (arrivals come from the peer CTA).
+HM_DEVICE bool mbar_wait_bounded_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  uint64_t t0 = 0;
+  for (uint32_t spin = 1;; ++spin) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if ((spin & 0xFF) == 0) {
+      if (*abort_flag) return false;
+      uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitLimitNs) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+// Shared-memory address of the same offset in the pair's leader CTA (rank 0):
+// inside a 2-CTA cluster the rank is bit 24 of a shared::cluster address.
+HM_DEVICE uint32_t leader_smem_addr(uint32_t addr) { return addr & 0xFEFFFFFFu; }
+
 // ---------------------------------------------------------------- fences
 HM_DEVICE void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -150,6 +201,16 @@ HM_DEVICE void tma_load_2d(uint32_t dst, const CUtensorMap* tmap, int x, int y, 
       "l"(tmap), "r"(x), "r"(y), "r"(bar)
       : "memory");
 }
+// Same for a CTA pair: the copy lands in this CTA's shared memory, the
+// transaction bytes are counted on the barrier `bar` in the leader CTA (pass
+// leader_smem_addr(local barrier address)).
+HM_DEVICE void tma_load_2d_pair(uint32_t dst, const CUtensorMap* tmap, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::
+          "r"(dst),
+      "l"(tmap), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
 HM_DEVICE void tma_prefetch_desc(const CUtensorMap* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
@@ -166,6 +227,23 @@ HM_DEVICE void tmem_relinquish() {
 HM_DEVICE void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
                : "memory");
+}
+HM_DEVICE void tmem_alloc_pair(uint32_t smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result), "r"(ncols)
+               : "memory");
+}
+HM_DEVICE void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+HM_DEVICE void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// Arrives on `bar` (same offset) in both CTAs of the pair once the pair's MMAs issued so far are done.
+HM_DEVICE void tc_commit_pair(uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .b16 m;\n\tmov.b16 m, 3;\n\t"
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], m;\n\t}" ::"r"(bar)
+      : "memory");
 }
 HM_DEVICE void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 HM_DEVICE void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -238,6 +316,61 @@ HM_DEVICE bool mma_step_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc
       "tcgen05.mma.cta_group::1.kind::f16 [%1], [a7], b7, %5, pone;\n\t"
       "SKIP_MMA_%=:\n\t"
       "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%7];\n\t"
+      "and.pred pna, pna, pnx;\n\t"
+      "selp.u32 %0, 1, 0, pna;\n\t"
+      "}"
+      : "=r"(ok)
+      : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(box_step), "r"(idesc), "r"(acc0), "r"(commit_bar), "r"(next_bar_a),
+        "r"(next_par_a), "r"(next_bar_x), "r"(next_par_x), "r"(static_cast<uint32_t>(skip_mma))
+      : "memory");
+  return ok != 0;
+}
+
+// The same step issued by the leader of a CTA pair: M = 256 (128 weight rows
+// from each CTA's tensor memory), each CTA's shared memory holds half of the
+// activation rows; the commit arrives on `commit_bar` in both CTAs.
+HM_DEVICE bool mma_step_f16_ts_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t box_step, uint32_t idesc,
+                                    uint32_t acc0, uint32_t commit_bar, uint32_t next_bar_a, uint32_t next_par_a,
+                                    uint32_t next_bar_x, uint32_t next_par_x, bool skip_mma) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred pacc, pone, pna, pnx, pskip;\n\t"
+      ".reg .b32 a1, a2, a3, a4, a5, a6, a7;\n\t"
+      ".reg .b64 b1, b2, b3, b4, b5, b6, b7, bs;\n\t"
+      ".reg .b16 cmask;\n\t"
+      "mov.b16 cmask, 3;\n\t"
+      "setp.ne.b32 pacc, %6, 0;\n\t"
+      "setp.eq.b32 pone, 0, 0;\n\t"
+      "setp.ne.b32 pskip, %12, 0;\n\t"
+      "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 pna, [%8], %9;\n\t"
+      "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 pnx, [%10], %11;\n\t"
+      "add.u32 a1, %2, 8;\n\t"
+      "add.u32 a2, %2, 16;\n\t"
+      "add.u32 a3, %2, 24;\n\t"
+      "add.u32 a4, %2, 32;\n\t"
+      "add.u32 a5, %2, 40;\n\t"
+      "add.u32 a6, %2, 48;\n\t"
+      "add.u32 a7, %2, 56;\n\t"
+      "cvt.u64.u32 bs, %4;\n\t"
+      "add.u64 b1, %3, 2;\n\t"
+      "add.u64 b2, %3, 4;\n\t"
+      "add.u64 b3, %3, 6;\n\t"
+      "add.u64 b4, %3, bs;\n\t"
+      "add.u64 b5, b4, 2;\n\t"
+      "add.u64 b6, b4, 4;\n\t"
+      "add.u64 b7, b4, 6;\n\t"
+      "@pskip bra SKIP_PAIR_MMA_%=;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%1], [%2], %3, %5, pacc;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%1], [a1], b1, %5, pone;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%1], [a2], b2, %5, pone;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%1], [a3], b3, %5, pone;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%1], [a4], b4, %5, pone;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%1], [a5], b5, %5, pone;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%1], [a6], b6, %5, pone;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%1], [a7], b7, %5, pone;\n\t"
+      "SKIP_PAIR_MMA_%=:\n\t"
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%7], cmask;\n\t"
       "and.pred pna, pna, pnx;\n\t"
       "selp.u32 %0, 1, 0, pna;\n\t"
       "}"

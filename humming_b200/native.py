@@ -20,6 +20,8 @@ HM_STATIC_SCRATCH_BYTES = 8 << 20
 
 HM_FLAG_A_OPERAND_SMEM = 1
 HM_FLAG_NO_SPLIT_K = 2
+HM_FLAG_CTA_PAIR = 4
+HM_FLAG_NO_CTA_PAIR = 8
 
 
 class GemmDesc(ctypes.Structure):
@@ -34,7 +36,7 @@ class Plan(ctypes.Structure):
     """``hm_plan``."""
 
     _fields_ = [(n, ctypes.c_int32) for n in (
-        "m_tile", "n_tiles", "m_tiles", "kb_per_tile", "mode", "grid", "units_per_cta", "reserved")] + [
+        "m_tile", "n_tiles", "m_tiles", "kb_per_tile", "mode", "grid", "units_per_cta", "cta_pair")] + [
         ("total_units", ctypes.c_int64), ("workspace_bytes", ctypes.c_int64)]
 
 

@@ -77,18 +77,26 @@ typedef struct hm_gemm_desc {
 /* Never split a tile's K range over several CTAs (batch-invariant results, the
  * counterpart of use_stream_k=False, docs/CONFIG.md "Scheduler Config"). */
 #define HM_FLAG_NO_SPLIT_K 2
+/* Dense GEMM on clusters of two CTAs sharing one 256-row weight tile
+ * (tcgen05 cta_group::2: half the MMA instructions per SM, each CTA loads half
+ * of the activation tile).  Needs shape_n % 256 == 0, integer 4-bit weights and
+ * a token tile of 32, 64, 128 or 256; otherwise the single-CTA kernel runs.
+ * HM_FLAG_CTA_PAIR asks for it, HM_FLAG_NO_CTA_PAIR forbids it; with neither the
+ * plan decides.  No counterpart in the reference (one CTA per tile there). */
+#define HM_FLAG_CTA_PAIR 4
+#define HM_FLAG_NO_CTA_PAIR 8
 
 /* Launch plan chosen for (desc, m); returned by hm_gemm_plan for tests,
  * benchmarks and workspace sizing. */
 typedef struct hm_plan {
   int32_t m_tile;         /* tokens per tile (UMMA N)                          */
-  int32_t n_tiles;        /* shape_n / 128                                     */
+  int32_t n_tiles;        /* shape_n / 128 (shape_n / 256 with cta_pair)       */
   int32_t m_tiles;
   int32_t kb_per_tile;    /* shape_k / 128: K steps per tile                   */
   int32_t mode;           /* 0 = whole tiles round-robin, 1 = contiguous K-split */
-  int32_t grid;           /* CTAs launched                                     */
+  int32_t grid;           /* workers scheduled: CTAs, or CTA pairs with cta_pair */
   int32_t units_per_cta;  /* mode 1: (tile, K step) units per CTA              */
-  int32_t reserved;
+  int32_t cta_pair;       /* 1: clusters of two CTAs, 256 weight rows per tile */
   int64_t total_units;
   int64_t workspace_bytes;
 } hm_plan;
@@ -255,7 +263,9 @@ HM_API int hm_debug_schedule(const hm_plan* plan, int cta, int32_t* out, int cap
 
 /* Development aid: while `device_buffer` is non-NULL, CTA 0 of every hm_gemm
  * launch writes clock64() timestamps of its pipeline roles into it
- * (8 roles x 128 k-blocks x 4 stamps x 8 bytes = 32 KB); `experiment_flags`
+ * (8 roles x 128 k-blocks x 4 stamps x 8 bytes = 32 KB) and every CTA
+ * (the first 1024) appends its %globaltimer entry and exit time (16 KB more,
+ * so the buffer is 48 KB); `experiment_flags`
  * switches individual pipeline steps off for timing experiments (results are
  * then wrong).  Pass (NULL, 0) to restore normal operation.  Process-wide, not
  * thread-safe. */

@@ -71,11 +71,12 @@ def test_static_scratch_matches_workspace_path_twice(cuda_device):
 
 
 def test_static_scratch_refuses_shapes_beyond_its_size(cuda_device):
-    case = synthetic.dense_w4a16_case(4096, 4096, torch.bfloat16, True, seed=31)
+    # a long K with few tiles: planned as a K split whose partial tiles exceed the static array
+    case = synthetic.dense_w4a16_case(2048, 8192, torch.bfloat16, True, seed=31)
     layer, _ = build_layer(case)
     desc = HummingMethod._desc(layer.meta)
-    x = synthetic.activations(256, 4096, torch.bfloat16).to(cuda_device)
-    out = torch.empty((256, 4096), dtype=torch.bfloat16, device=cuda_device)
+    x = synthetic.activations(256, 8192, torch.bfloat16).to(cuda_device)
+    out = torch.empty((256, 2048), dtype=torch.bfloat16, device=cuda_device)
     plan = native.Plan()
     native.check(native.lib.hm_gemm_plan(ctypes.byref(desc), 256, ctypes.byref(plan)))
     assert plan.workspace_bytes > native.HM_STATIC_SCRATCH_BYTES

@@ -639,7 +639,7 @@ int64_t moe_workspace_bytes(const hm_gemm_desc* d, int64_t capacity, int mt, int
 }
 
 template <int MT, bool BF16, bool HAS_ZP>
-int launch_moe(const hm::GemmParams& p, int grid, cudaStream_t stream) {
+int launch_moe(const hm::GemmParams& p, const CUtensorMap& tmap, int grid, cudaStream_t stream) {
   using Cfg = hm::GemmCfg<MT, true>;
   auto kern = hm::gemm_w4a16_kernel<MT, BF16, HAS_ZP, true, true>;
   static bool configured[64] = {false};
@@ -650,17 +650,15 @@ int launch_moe(const hm::GemmParams& p, int grid, cudaStream_t stream) {
     HM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
     configured[dev & 63] = true;
   }
-  CUtensorMap unused;
-  memset(&unused, 0, sizeof(unused));
-  kern<<<grid, Cfg::THREADS, Cfg::SMEM_ALLOC, stream>>>(p, unused);
+  kern<<<grid, Cfg::THREADS, Cfg::SMEM_ALLOC, stream>>>(p, tmap);
   HM_CUDA_OK(cudaGetLastError());
   return HM_OK;
 }
 
 template <int MT>
-int dispatch_moe(bool bf16, bool zp, const hm::GemmParams& p, int grid, cudaStream_t stream) {
-  if (bf16) return zp ? launch_moe<MT, true, true>(p, grid, stream) : launch_moe<MT, true, false>(p, grid, stream);
-  return zp ? launch_moe<MT, false, true>(p, grid, stream) : launch_moe<MT, false, false>(p, grid, stream);
+int dispatch_moe(bool bf16, bool zp, const hm::GemmParams& p, const CUtensorMap& tmap, int grid, cudaStream_t stream) {
+  if (bf16) return zp ? launch_moe<MT, true, true>(p, tmap, grid, stream) : launch_moe<MT, true, false>(p, tmap, grid, stream);
+  return zp ? launch_moe<MT, false, true>(p, tmap, grid, stream) : launch_moe<MT, false, false>(p, tmap, grid, stream);
 }
 
 }  // namespace
@@ -671,23 +669,27 @@ int hm_moe_align_block_size(const int32_t* topk_ids, int64_t numel, int num_expe
                             void* stream) {
   if (topk_ids == nullptr || sorted_ids == nullptr || expert_ids == nullptr || num_post_padded == nullptr || scratch == nullptr)
     return fail(HM_ERR_INVALID, "NULL pointer");
-  if (numel <= 0 || numel > (1ll << 30) || num_experts <= 0 || num_experts > 65536 || block <= 0)
+  if (numel <= 0 || numel > (1ll << 30) || num_experts <= 0 || block <= 0)
     return fail(HM_ERR_INVALID, "bad numel / num_experts / block");
   const int64_t need = ((numel + static_cast<int64_t>(num_experts) * (block - 1) + block - 1) / block) * block;
   if (capacity % block != 0 || capacity < need)
     return fail(HM_ERR_INVALID, "sorted_ids capacity %lld too small: %lld needed (numel + experts * (block - 1), rounded up to the block)",
                 static_cast<long long>(capacity), static_cast<long long>(need));
+  if (num_experts > hm::kAlignMaxExperts) return fail(HM_ERR_UNSUPPORTED, "at most %d experts", hm::kAlignMaxExperts);
   auto s = static_cast<cudaStream_t>(stream);
-  int* counts = scratch;
-  int* offsets = scratch + num_experts;
-  HM_CUDA_OK(cudaMemsetAsync(counts, 0, sizeof(int) * num_experts, s));
+  const int chunks = static_cast<int>((numel + hm::kAlignChunk - 1) / hm::kAlignChunk);
   HM_CUDA_OK(cudaMemsetAsync(expert_ids, 0, sizeof(int) * (capacity / block), s));
-  hm::moe_count_kernel<<<blocks_for(numel, 256), 256, 0, s>>>(topk_ids, static_cast<int>(numel), num_experts, counts);
-  hm::moe_scan_kernel<<<1, 1024, 0, s>>>(counts, num_experts, block, static_cast<int>(numel), static_cast<int>(capacity),
-                                         offsets, expert_ids, num_post_padded, sorted_ids);
-  hm::moe_scatter_kernel<<<(num_experts + 7) / 8, 256, 0, s>>>(topk_ids, static_cast<int>(numel), num_experts, offsets, sorted_ids);
+  hm::moe_align_hist_kernel<<<chunks, hm::kAlignChunk, 0, s>>>(topk_ids, static_cast<int>(numel), num_experts, static_cast<int>(capacity),
+                                                              scratch, sorted_ids);
+  hm::moe_align_scan_kernel<<<1, 1024, 0, s>>>(scratch, chunks, num_experts, block, expert_ids, num_post_padded);
+  hm::moe_align_place_kernel<<<chunks, hm::kAlignChunk, 0, s>>>(topk_ids, static_cast<int>(numel), num_experts, scratch, sorted_ids);
   HM_CUDA_OK(cudaGetLastError());
   return HM_OK;
+}
+
+int64_t hm_moe_align_scratch_ints(int64_t numel, int num_experts) {
+  if (numel <= 0 || num_experts <= 0) return 0;
+  return ((numel + hm::kAlignChunk - 1) / hm::kAlignChunk) * static_cast<int64_t>(num_experts);
 }
 
 size_t hm_moe_gemm_workspace_bytes(const hm_gemm_desc* desc, int64_t capacity) {
@@ -773,10 +775,12 @@ int hm_moe_gemm(const hm_gemm_desc* desc, int64_t num_valid, const void* a, int6
   p.num_valid = static_cast<int>(num_valid);
   p.max_m_tiles = static_cast<int>(capacity / mt);
   p.min_units = 2;
+  p.a_sorted = (desc->flags & HM_FLAG_MOE_A_SORTED) ? 1 : 0;
+  p.c_sorted = (desc->flags & HM_FLAG_MOE_C_SORTED) ? 1 : 0;
   const bool bf16 = desc->c_dtype == HM_BF16;
   auto s = static_cast<cudaStream_t>(stream);
   if (a_fp8) {
-    const int64_t rows = desc->is_moe_down ? num_valid : num_valid / desc->top_k;
+    const int64_t rows = p.a_sorted ? capacity : (desc->is_moe_down ? num_valid : num_valid / desc->top_k);
     if (rows > capacity) return fail(HM_ERR_WORKSPACE, "more activation rows than the workspace was sized for");
     auto dst = reinterpret_cast<uint16_t*>(ws + moe_core_bytes(desc, capacity, mt, sms));
     const unsigned blocks = blocks_for(rows * desc->shape_k / 8, 256);
@@ -788,11 +792,26 @@ int hm_moe_gemm(const hm_gemm_desc* desc, int64_t num_valid, const void* a, int6
     p.lda = desc->shape_k;
     p.act_scale = a_scale;
   }
+  // Activations already in the order of sorted_ids are loaded as tiles by TMA, like the dense GEMM's.
+  CUtensorMap tmap;
+  memset(&tmap, 0, sizeof(tmap));
+  if (p.a_sorted) {
+    auto encode = tensor_map_encoder();
+    if (encode == nullptr) return fail(HM_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(desc->shape_k), static_cast<cuuint64_t>(capacity)};
+    const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(p.lda) * 2};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(hm::kBlockK), static_cast<cuuint32_t>(mt)};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult cr = encode(&tmap, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(p.a), gdim,
+                         gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) return fail(HM_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", static_cast<int>(cr));
+  }
   switch (mt) {
-    case 16: return dispatch_moe<16>(bf16, desc->has_zp != 0, p, sms, s);
-    case 32: return dispatch_moe<32>(bf16, desc->has_zp != 0, p, sms, s);
-    case 64: return dispatch_moe<64>(bf16, desc->has_zp != 0, p, sms, s);
-    case 128: return dispatch_moe<128>(bf16, desc->has_zp != 0, p, sms, s);
+    case 16: return dispatch_moe<16>(bf16, desc->has_zp != 0, p, tmap, sms, s);
+    case 32: return dispatch_moe<32>(bf16, desc->has_zp != 0, p, tmap, sms, s);
+    case 64: return dispatch_moe<64>(bf16, desc->has_zp != 0, p, tmap, sms, s);
+    case 128: return dispatch_moe<128>(bf16, desc->has_zp != 0, p, tmap, sms, s);
   }
   return fail(HM_ERR_INVALID, "no MoE kernel for token tile %d", mt);
 }
@@ -809,15 +828,43 @@ int hm_moe_route(const float* logits, int64_t tokens, int experts, int top_k, in
   return HM_OK;
 }
 
+int hm_moe_gather_rows(const void* a, int64_t lda_bytes, int64_t row_bytes, const int32_t* sorted_ids, int64_t capacity,
+                       int64_t num_valid, int div, void* out, int64_t ldo_bytes, void* stream) {
+  if (a == nullptr || sorted_ids == nullptr || out == nullptr) return fail(HM_ERR_INVALID, "NULL pointer");
+  if (capacity < 0 || num_valid < 0 || num_valid > (1ll << 30) || div <= 0 || row_bytes <= 0 || row_bytes > (1 << 30))
+    return fail(HM_ERR_INVALID, "bad capacity / num_valid / div / row_bytes");
+  if ((row_bytes & 15) || (lda_bytes & 15) || (ldo_bytes & 15) || ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(out)) & 15))
+    return fail(HM_ERR_INVALID, "rows must be 16-byte aligned and a multiple of 16 bytes long");
+  if (lda_bytes < row_bytes || ldo_bytes < row_bytes) return fail(HM_ERR_INVALID, "row pitch smaller than the row length");
+  if (capacity == 0) return HM_OK;
+  const unsigned blocks = blocks_for(capacity * (row_bytes / 16), 256);
+  hm::moe_gather_rows_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(a), lda_bytes, static_cast<int>(row_bytes), sorted_ids, capacity, static_cast<int>(num_valid), div,
+      static_cast<uint8_t*>(out), ldo_bytes);
+  HM_CUDA_OK(cudaGetLastError());
+  return HM_OK;
+}
+
 int hm_silu_mul(const void* x, void* out, int64_t rows, int inter, int dtype, void* stream) {
   if (x == nullptr || out == nullptr) return fail(HM_ERR_INVALID, "NULL pointer");
   if (rows < 0 || inter <= 0) return fail(HM_ERR_INVALID, "bad rows / inter");
   if (rows == 0) return HM_OK;
   auto s = static_cast<cudaStream_t>(stream);
-  const unsigned blocks = blocks_for(rows * inter, 256);
-  if (dtype == HM_BF16) hm::silu_mul_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(out), rows, inter);
-  else if (dtype == HM_F16) hm::silu_mul_kernel<__half><<<blocks, 256, 0, s>>>(static_cast<const __half*>(x), static_cast<__half*>(out), rows, inter);
-  else return fail(HM_ERR_INVALID, "dtype code %d not accepted", dtype);
+  if (dtype != HM_BF16 && dtype != HM_F16) return fail(HM_ERR_INVALID, "dtype code %d not accepted", dtype);
+  // 16-byte accesses when the row length and both buffers allow it.
+  const bool vec = inter % 8 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  const unsigned blocks = blocks_for(rows * (vec ? inter / 8 : inter), 256);
+  if (dtype == HM_BF16) {
+    auto xi = static_cast<const __nv_bfloat16*>(x);
+    auto oi = static_cast<__nv_bfloat16*>(out);
+    if (vec) hm::silu_mul_kernel<__nv_bfloat16, 8><<<blocks, 256, 0, s>>>(xi, oi, rows, inter);
+    else hm::silu_mul_kernel<__nv_bfloat16, 1><<<blocks, 256, 0, s>>>(xi, oi, rows, inter);
+  } else {
+    auto xi = static_cast<const __half*>(x);
+    auto oi = static_cast<__half*>(out);
+    if (vec) hm::silu_mul_kernel<__half, 8><<<blocks, 256, 0, s>>>(xi, oi, rows, inter);
+    else hm::silu_mul_kernel<__half, 1><<<blocks, 256, 0, s>>>(xi, oi, rows, inter);
+  }
   HM_CUDA_OK(cudaGetLastError());
   return HM_OK;
 }
@@ -827,10 +874,20 @@ int hm_topk_sum(const void* x, void* out, int64_t tokens, int top_k, int width, 
   if (tokens < 0 || top_k <= 0 || width <= 0) return fail(HM_ERR_INVALID, "bad tokens / top_k / width");
   if (tokens == 0) return HM_OK;
   auto s = static_cast<cudaStream_t>(stream);
-  const unsigned blocks = blocks_for(tokens * width, 256);
-  if (dtype == HM_BF16) hm::topk_sum_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(out), tokens, top_k, width);
-  else if (dtype == HM_F16) hm::topk_sum_kernel<__half><<<blocks, 256, 0, s>>>(static_cast<const __half*>(x), static_cast<__half*>(out), tokens, top_k, width);
-  else return fail(HM_ERR_INVALID, "dtype code %d not accepted", dtype);
+  if (dtype != HM_BF16 && dtype != HM_F16) return fail(HM_ERR_INVALID, "dtype code %d not accepted", dtype);
+  const bool vec = width % 8 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  const unsigned blocks = blocks_for(tokens * (vec ? width / 8 : width), 256);
+  if (dtype == HM_BF16) {
+    auto xi = static_cast<const __nv_bfloat16*>(x);
+    auto oi = static_cast<__nv_bfloat16*>(out);
+    if (vec) hm::topk_sum_kernel<__nv_bfloat16, 8><<<blocks, 256, 0, s>>>(xi, oi, tokens, top_k, width);
+    else hm::topk_sum_kernel<__nv_bfloat16, 1><<<blocks, 256, 0, s>>>(xi, oi, tokens, top_k, width);
+  } else {
+    auto xi = static_cast<const __half*>(x);
+    auto oi = static_cast<__half*>(out);
+    if (vec) hm::topk_sum_kernel<__half, 8><<<blocks, 256, 0, s>>>(xi, oi, tokens, top_k, width);
+    else hm::topk_sum_kernel<__half, 1><<<blocks, 256, 0, s>>>(xi, oi, tokens, top_k, width);
+  }
   HM_CUDA_OK(cudaGetLastError());
   return HM_OK;
 }

@@ -87,6 +87,8 @@ struct GemmParams {
   int num_valid;               // tokens * top_k; ids >= num_valid are padding
   int max_m_tiles;             // capacity of sorted_ids in token tiles
   int min_units;               // smallest K-split worth a CTA
+  int a_sorted;                // 1: a holds one row per entry of sorted_ids, in that order (tiled TMA loads, no gather)
+  int c_sorted;                // 1: c gets one row per entry of sorted_ids, in that order (padding rows included)
   // ---- 8-bit activations (converted to the 16-bit compute type beforehand) ----
   const float* act_scale;      // per activation row fp32 scale, multiplied into the output, or null
 };
@@ -109,26 +111,40 @@ struct GemmCfg {
   // the warps and ring slots each) so that two issue streams interleave.
   static constexpr bool DUAL = A_TMEM && MT <= 64 && !PAIR;
   static constexpr int CTAS_PER_SM = DUAL ? 2 : 1;
-  static constexpr int SA = (!A_TMEM || MT == 192 || DUAL) ? 2 : 4;
+#ifndef HM_DUAL_SA
+#define HM_DUAL_SA 3
+#endif
+  // Two CTAs per SM: half of the tensor memory (256 columns) each.  Three operand
+  // slots of 64 columns fit beside the accumulators (one accumulator only for the
+  // 64-token tile); two dequant groups fill them in turn.
+  static constexpr int SA = DUAL ? HM_DUAL_SA : ((!A_TMEM || MT == 192) ? 2 : 4);
   // An activation stage is normally released by the same tcgen05.commit as the
   // operand slot of its step (one commit per step), so its ring cannot be deeper
   // than SA.  With two CTAs per SM only two operand slots fit, which is too
   // shallow to hide the latency of the activation loads (about 1300 cycles
   // against steps of 800): there the ring gets barriers and a commit of its own.
   static constexpr bool X_OWN_RING = DUAL;
-  static constexpr int SX = X_OWN_RING ? (MT <= 32 ? 8 : 4) : ((MT <= 128 || PAIR) ? SA : 2);
-  static constexpr int SW = DUAL ? 4 : (MT <= 64 ? 8 : 4);
+  // The 256-token tile has a single accumulator, so the MMAs of the next tile wait
+  // while the epilogue drains it.  The CTA pair (half the activation bytes per CTA)
+  // has room to stage the whole converted tile in shared memory: the accumulator
+  // is handed back after the TMEM -> shared copy and the global stores overlap the
+  // next tile's main loop.
+  static constexpr bool STAGED_EPI = PAIR && MT == 256;
+  static constexpr int SX = X_OWN_RING ? (HM_DUAL_SA == 3 ? (MT <= 16 ? 8 : MT <= 32 ? 4 : 3) : (MT <= 32 ? 8 : 4))
+                                       : (STAGED_EPI ? 3 : ((MT <= 128 || PAIR) ? SA : 2));
+  static constexpr int SW = DUAL ? (HM_DUAL_SA == 3 ? 6 : 4) : (MT <= 64 ? 8 : 4);
   // Dequant warp groups (4 warps each) taking stages round-robin.  A slot (and a
   // weight stage) must always be refilled by the group that filled it before:
   // phase-parity waits cannot tell a barrier that is two phases behind from one
   // that is current, so no group may run ahead of another on the same barrier.
-  static constexpr int NGROUPS = SA;
+  static constexpr int NGROUPS = DUAL ? 2 : SA;
   static constexpr int EPI_WARP0 = 4 + 4 * NGROUPS;
   static constexpr int THREADS = (EPI_WARP0 + 4) * 32;
   static constexpr int A_SLOT_COLS = kStageK / 2;  // 64 columns of packed 16-bit pairs
   // Two accumulators let the epilogue of one tile overlap the main loop of the
   // next; the 256-token tile has no TMEM left for a second one.
-  static constexpr int ACC_BUFS = (2 * MT + (A_TMEM ? SA * A_SLOT_COLS : 0) <= 512) ? 2 : 1;
+  static constexpr int TMEM_LIMIT = DUAL ? 256 : 512;
+  static constexpr int ACC_BUFS = (2 * MT + (A_TMEM ? SA * A_SLOT_COLS : 0) <= TMEM_LIMIT) ? 2 : 1;
   static constexpr int A_COL0 = ACC_BUFS * MT;
   static constexpr int USED_COLS = A_COL0 + (A_TMEM ? SA * A_SLOT_COLS : 0);
   static constexpr int TMEM_COLS = USED_COLS <= 32 ? 32 : USED_COLS <= 64 ? 64 : USED_COLS <= 128 ? 128 : USED_COLS <= 256 ? 256 : 512;
@@ -140,15 +156,19 @@ struct GemmCfg {
   static constexpr int SMEM_X = 0;
   static constexpr int SMEM_A = SMEM_X + SX * X_STAGE;
   static constexpr int SMEM_W = SMEM_A + SA * A_STAGE;
-  static constexpr int SMEM_STAGE = SMEM_W + SW * kWStageBytes;  // epilogue transpose staging, 2 KB per warp
-  static constexpr int SMEM_BAR = SMEM_STAGE + 4 * 2048 + 1024;  // + gathered-row indices of the MoE producer
+  static constexpr int SMEM_STAGE = SMEM_W + SW * kWStageBytes;  // epilogue transpose staging, per warp [tokens][32 rows] x 16 bit
+  static constexpr int EPI_WARP_BYTES = STAGED_EPI ? MT * 64 : 2048;
+  static constexpr int SMEM_BAR = SMEM_STAGE + 4 * EPI_WARP_BYTES + 1024;  // + gathered-row indices of the MoE producer
   static constexpr int SMEM_TOTAL = SMEM_BAR + kNumBarrierSlots * 8 + 256;  // + TMEM address, abort flags, pending reductions
   static constexpr int SMEM_ALLOC = SMEM_TOTAL + 1024;  // slack for manual 1024-byte alignment
-  static_assert(USED_COLS <= 512, "tensor memory budget");
+  static_assert(USED_COLS <= TMEM_LIMIT, "tensor memory budget");
   static_assert(SMEM_ALLOC <= 232448, "shared memory budget");
   static_assert(!DUAL || SMEM_ALLOC <= 115712, "two CTAs per SM: half of the shared memory each");
   static_assert(2 * SW + 2 * SX + 2 * SA + 5 <= kNumBarrierSlots, "barrier slots");
-  static_assert(SA % NGROUPS == 0 && SW % NGROUPS == 0, "each ring slot belongs to one dequant group");
+  // Either every ring slot belongs to one dequant group, or (operand slots shared between groups) a group
+  // that reaches step i knows that step i - 2*SA has completed and that the weight stage of step i - SW has
+  // been consumed: it passed step i - NGROUPS, whose slot wait implies the MMAs of step i - NGROUPS - SA.
+  static_assert(SW % NGROUPS == 0 && (SA % NGROUPS == 0 || (NGROUPS <= SA && SW >= NGROUPS + SA)), "ring depths vs dequant groups");
   static_assert(X_OWN_RING || SX <= SA, "activation stages are released through the operand-slot barriers");
 };
 
@@ -259,7 +279,7 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
       mbar_init(w_empty(i), 4);
     }
     for (int i = 0; i < SX; ++i) {
-      mbar_init(x_full(i), 1);
+      mbar_init(x_full(i), (MOE && !p.a_sorted) ? 32 : 1);  // gathered rows: one arrival per lane of the producer warp
       mbar_init(x_empty(i), 1);
     }
     for (int i = 0; i < SA; ++i) {
@@ -287,7 +307,7 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
       tmem_relinquish();
     }
   }
-  if (!MOE && warp == 1 && lane == 0) tma_prefetch_desc(&tmap_x);
+  if ((!MOE || p.a_sorted) && warp == 1 && lane == 0) tma_prefetch_desc(&tmap_x);
   tc_fence_before();
   __syncthreads();
   if constexpr (PAIR) cluster_sync_all();  // the peer's barriers are initialised before anyone signals them
@@ -423,27 +443,37 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
         }
       }
     }
-  } else if (warp == 1 && MOE) {
+  } else if (warp == 1 && MOE && !p.a_sorted) {
     // ------------------------------------------------ activation producer, gathered rows (whole warp)
     // 8 lanes copy the 128 bytes of one row's 64-K slice, 4 rows per instruction;
     // 16-byte chunk c of row r lands at chunk (c ^ (r & 7)) of its 128-byte line,
     // 8-row groups 1024 bytes apart -- the layout of a 128-byte-swizzled TMA box.
-    // Copies of a stage form one cp.async group; a stage is published (proxy
-    // fence + arrive) once its group has landed, XLAG stages later (half the ring,
-    // so that the issuer of new copies stays ahead of the MMAs by the other half).
-    constexpr int XLAG = SX > 2 ? SX / 2 : SX - 1;
-    int* xrow = reinterpret_cast<int*>(smem_gen + Cfg::SMEM_STAGE + 4 * 2048);  // source row per token of the tile
+    // Every lane attaches the completion of its copies of a stage to the stage's
+    // barrier (cp.async.mbarrier.arrive, 32 arrivals per phase), so the warp never
+    // waits for data and the whole ring can be in flight.  (TMA tile::gather4
+    // measured slower than these copies: about 60 cycles per 512-byte instruction.)
+    // Byte offset of every token's source row (bit 0: the row exists; padding rows are zero-filled),
+    // computed once per tile so that a copy costs one shared-memory load and two adds.
+    unsigned long long* xoff = reinterpret_cast<unsigned long long*>(smem_gen + Cfg::SMEM_STAGE + 4 * Cfg::EPI_WARP_BYTES);
+    static_assert(!MOE || MT * 8 <= 1024, "row-offset table");
     Ring<SX> ring;      // stage being filled
-    Ring<SX> publish;   // oldest stage not yet published
     Ring<Cfg::X_OWN_RING ? SX : SA> done;  // barrier whose completion frees stage ring.idx (step it - SX)
-    int it = 0, published = 0;
+    int it = 0;
     bool ok = true;
     const int sub_row = lane >> 3, chunk = lane & 7;
+    // Row r = 4 * i + sub_row: r & 7 takes two values per lane (i even / odd), r >> 3 = i >> 1.
+    uint32_t lane_off[2];
+#pragma unroll
+    for (int par = 0; par < 2; ++par) {
+      const int r7 = par * 4 + sub_row;
+      lane_off[par] = r7 * 128 + ((chunk ^ r7) * 16);
+    }
     while (ok && iter.next(seg)) {
       __syncwarp();
       for (int r = lane; r < MT; r += 32) {
         const int id = p.sorted_ids[seg.m_tile * MT + r];
-        xrow[r] = id < p.num_valid ? (p.is_down ? id : id / p.top_k) : -1;
+        const int src_row = id < p.num_valid ? (p.is_down ? id : id / p.top_k) : -1;
+        xoff[r] = src_row < 0 ? 0ull : ((static_cast<unsigned long long>(src_row) * p.lda * 2) | 1ull);
       }
       __syncwarp();
       int col = seg.kb0 * kStageK;
@@ -456,41 +486,26 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
           }
           done.advance();
         }
+        if (lane == 0) trace(1, it, 0);
         const uint32_t dst0 = x_smem + ring.idx * Cfg::X_STAGE;
+        const uint8_t* a_col = static_cast<const uint8_t*>(p.a) + (col + chunk * 8) * 2;
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-#pragma unroll
-          for (int i = 0; i < MT / 4; ++i) {
-            const int r = i * 4 + sub_row;
-            const int src_row = xrow[r];
-            const uint8_t* src = static_cast<const uint8_t*>(p.a) +
-                                 (static_cast<size_t>(src_row < 0 ? 0 : src_row) * p.lda + col + h * kBlockK + chunk * 8) * 2;
-            const uint32_t dst = dst0 + h * Cfg::X_BOX + (r >> 3) * 1024 + (r & 7) * 128 + ((chunk ^ (r & 7)) * 16);
-            cp_async_16(dst, src, src_row < 0 ? 0u : 16u);
-          }
+        for (int i = 0; i < MT / 4; ++i) {
+          const unsigned long long e = xoff[i * 4 + sub_row];
+          const uint8_t* src = a_col + (e & ~1ull);
+          const uint32_t bytes = (e & 1ull) ? 16u : 0u;
+          const uint32_t dst = dst0 + (i >> 1) * 1024 + lane_off[i & 1];
+          cp_async_16(dst, src, bytes);
+          cp_async_16(dst + Cfg::X_BOX, src + kBlockK * 2, bytes);
         }
-        cp_async_commit();
+        cp_async_mbar_arrive_noinc(x_full(ring.idx));
+        if (lane == 0) trace(1, it, 1);
         col += kStageK;
         ring.advance();
-        if (it - published >= XLAG) {
-          cp_async_wait<XLAG>();
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(x_full(publish.idx));
-          publish.advance();
-          ++published;
-        }
       }
     }
-    // Publish what is still in flight (also on the abort path, so nothing lands after exit).
-    cp_async_wait<0>();
-    fence_proxy_async_smem();
-    __syncwarp();
-    while (ok && published < it) {
-      if (lane == 0) mbar_arrive(x_full(publish.idx));
-      publish.advance();
-      ++published;
-    }
+    // Nothing may land after the CTA has exited (also on the abort path).
+    cp_async_wait_all();
   } else if (warp == 1) {
     // ------------------------------------------------ activation producer
     if (lane == 0) {
@@ -571,6 +586,8 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
             }
           }
           trace(2, it, 1);
+          // Gathered rows were written by cp.async; the MMA reads them through the async proxy.
+          if (MOE && !p.a_sorted) fence_proxy_async_smem();
           tc_fence_after();
           const uint32_t slot = ra.idx;
           const uint32_t xs = rx.idx;
@@ -746,7 +763,8 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
       float* slot = p.partials + static_cast<size_t>(seg.slot * slot_mul + rank) * (MT * kTileN);
       const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + b * MT;
       constexpr int CH = MT >= 32 ? 32 : 16;  // token columns per chunk
-      uint8_t* stage = smem_gen + Cfg::SMEM_STAGE + q * 2048;  // this warp's [CH tokens][32 rows] 16-bit tile
+      // This warp's [tokens][32 rows] 16-bit tile: one chunk of CH tokens, or the whole tile when staged.
+      uint8_t* stage_base = smem_gen + Cfg::SMEM_STAGE + q * Cfg::EPI_WARP_BYTES;
 #pragma unroll 1
       for (int c0 = 0; c0 < MT; c0 += CH) {
         if (c0 >= m_valid) break;  // warp-uniform
@@ -770,12 +788,15 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
           float out_w = 1.f;   // MoE down projection: its routing weight
           float col_s = 1.f;   // 8-bit activations: the token's quantization scale
           if constexpr (MOE) {
-            out_id = (lane < CH) ? p.sorted_ids[m0 + c0 + lane] : p.num_valid;
+            const int pos = m0 + c0 + lane;  // position in sorted_ids
+            out_id = (lane < CH) ? p.sorted_ids[pos] : p.num_valid;
             if (p.is_down && out_id < p.num_valid) out_w = p.topk_weights[out_id];
-            if (p.act_scale != nullptr && out_id < p.num_valid) col_s = p.act_scale[p.is_down ? out_id : out_id / p.top_k];
+            if (p.act_scale != nullptr && out_id < p.num_valid) col_s = p.act_scale[p.a_sorted ? pos : (p.is_down ? out_id : out_id / p.top_k)];
+            if (p.c_sorted) out_id = pos;  // output rows in sorted order, padding rows included
           } else if (p.act_scale != nullptr) {
             if (lane < CH && c0 + lane < m_valid) col_s = p.act_scale[m0 + c0 + lane];
           }
+          uint8_t* stage = stage_base + (Cfg::STAGED_EPI ? c0 * 64 : 0);
           __syncwarp();
 #pragma unroll
           for (int j = 0; j < CH; ++j) {
@@ -790,13 +811,13 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
           __syncwarp();
           const int n_base = ntile(seg) * kTileN + q * 32;
 #pragma unroll
-          for (int i = 0; i < CH / 8; ++i) {
+          for (int i = 0; i < (Cfg::STAGED_EPI ? 0 : CH / 8); ++i) {
             const int j = i * 8 + (lane >> 2);
             int out_row = m0 + c0 + j;
             bool valid = c0 + j < m_valid;
             if constexpr (MOE) {
               out_row = __shfl_sync(0xffffffffu, out_id, j);
-              valid = out_row < p.num_valid;
+              valid = p.c_sorted || out_row < p.num_valid;
             }
             if (valid) {
               const uint4 val = *reinterpret_cast<const uint4*>(stage + j * 64 + (lane & 3) * 16);
@@ -819,6 +840,18 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
       }
       if (q == 0 && lane == 0) trace(7, sc + 1, 1);
       ++sc;
+      if constexpr (Cfg::STAGED_EPI) {
+        // Staged tile -> global memory, while the MMAs of the next tile already run.
+        if (!seg.partial) {
+          const int n_base = ntile(seg) * kTileN + q * 32;
+          for (int j = lane >> 2; j < m_valid; j += 8) {
+            const uint4 val = *reinterpret_cast<const uint4*>(stage_base + j * 64 + (lane & 3) * 16);
+            uint8_t* dst = static_cast<uint8_t*>(p.c) + (static_cast<size_t>(m0 + j) * p.ldc + n_base) * 2 + (lane & 3) * 16;
+            *reinterpret_cast<uint4*>(dst) = val;
+          }
+          __syncwarp();
+        }
+      }
 
       if (seg.partial) {
         // Publish this warp's quarter of the partial tile, then find out whether
@@ -904,9 +937,13 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
         float sc_tok = 1.f, w_tok = 1.f;
         if constexpr (MOE) {
           out_row = p.sorted_ids[m0 + tok];
-          if (out_row >= p.num_valid) continue;
-          if (p.act_scale != nullptr) sc_tok = p.act_scale[p.is_down ? out_row : out_row / p.top_k];
-          if (p.is_down) w_tok = p.topk_weights[out_row];
+          if (out_row >= p.num_valid) {
+            if (!p.c_sorted) continue;
+          } else {
+            if (p.act_scale != nullptr) sc_tok = p.act_scale[p.a_sorted ? m0 + tok : (p.is_down ? out_row : out_row / p.top_k)];
+            if (p.is_down) w_tok = p.topk_weights[out_row];
+          }
+          if (p.c_sorted) out_row = m0 + tok;
         } else {
           if (p.act_scale != nullptr) sc_tok = p.act_scale[out_row];
         }

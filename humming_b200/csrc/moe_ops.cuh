@@ -96,28 +96,108 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int tokens, i
   }
 }
 
-// out[r, j] = silu(x[r, j]) * x[r, inter + j], x is [rows, 2*inter] = [gate | up].
+// Eight 16-bit values (one 16-byte load) <-> floats.
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t rows, int inter) {
-  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (i >= rows * inter) return;
-  const int64_t r = i / inter;
-  const int j = static_cast<int>(i - r * inter);
-  const float g = ld_as_float<T>(x + r * 2 * inter + j);
-  const float u = ld_as_float<T>(x + r * 2 * inter + inter + j);
-  st_from_float<T>(out + i, g / (1.f + __expf(-g)) * u);
+__device__ __forceinline__ void unpack8(const uint4& v, float* f);
+template <>
+__device__ __forceinline__ void unpack8<__nv_bfloat16>(const uint4& v, float* f) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+template <>
+__device__ __forceinline__ void unpack8<__half>(const uint4& v, float* f) {
+  const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __half22float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+template <typename T>
+__device__ __forceinline__ uint4 pack8(const float* f);
+template <>
+__device__ __forceinline__ uint4 pack8<__nv_bfloat16>(const float* f) {
+  uint4 v;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return v;
+}
+template <>
+__device__ __forceinline__ uint4 pack8<__half>(const float* f) {
+  uint4 v;
+  __half2* h = reinterpret_cast<__half2*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+  return v;
 }
 
-// out[t, j] = sum_k x[t, k, j]   (fp32 accumulation)
-template <typename T>
-__global__ void topk_sum_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t tokens, int top_k, int width) {
+// out[r, j] = silu(x[r, j]) * x[r, inter + j], x is [rows, 2*inter] = [gate | up].
+// VEC = 8: one thread per 8 consecutive j (inter % 8 == 0, 16-byte aligned buffers); VEC = 1: any inter.
+template <typename T, int VEC>
+__global__ void silu_mul_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t rows, int inter) {
+  const int per_row = inter / VEC;
   const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (i >= tokens * width) return;
-  const int64_t t = i / width;
-  const int j = static_cast<int>(i - t * width);
-  float acc = 0.f;
-  for (int k = 0; k < top_k; ++k) acc += ld_as_float<T>(x + (t * top_k + k) * width + j);
-  st_from_float<T>(out + i, acc);
+  if (i >= rows * per_row) return;
+  const int64_t r = i / per_row;
+  const int j = static_cast<int>(i - r * per_row) * VEC;
+  if constexpr (VEC == 8) {
+    float g[8], u[8], o[8];
+    unpack8<T>(*reinterpret_cast<const uint4*>(x + r * 2 * inter + j), g);
+    unpack8<T>(*reinterpret_cast<const uint4*>(x + r * 2 * inter + inter + j), u);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[e] = g[e] / (1.f + __expf(-g[e])) * u[e];
+    *reinterpret_cast<uint4*>(out + r * inter + j) = pack8<T>(o);
+  } else {
+    const float g = ld_as_float<T>(x + r * 2 * inter + j);
+    const float u = ld_as_float<T>(x + r * 2 * inter + inter + j);
+    st_from_float<T>(out + r * inter + j, g / (1.f + __expf(-g)) * u);
+  }
+}
+
+// out[t, j] = sum_k x[t, k, j]   (fp32 accumulation, k ascending)
+template <typename T, int VEC>
+__global__ void topk_sum_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t tokens, int top_k, int width) {
+  const int per_row = width / VEC;
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= tokens * per_row) return;
+  const int64_t t = i / per_row;
+  const int j = static_cast<int>(i - t * per_row) * VEC;
+  if constexpr (VEC == 8) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < top_k; ++k) {
+      float v[8];
+      unpack8<T>(*reinterpret_cast<const uint4*>(x + (t * top_k + k) * width + j), v);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += v[e];
+    }
+    *reinterpret_cast<uint4*>(out + t * width + j) = pack8<T>(acc);
+  } else {
+    float acc = 0.f;
+    for (int k = 0; k < top_k; ++k) acc += ld_as_float<T>(x + (t * top_k + k) * width + j);
+    st_from_float<T>(out + t * width + j, acc);
+  }
+}
+
+// out[i, :] = a[sorted_ids[i] / div, :] for real entries, zeros for padding entries
+// (sorted_ids[i] >= num_valid); rows are row_bytes long, a multiple of 16 bytes.
+__global__ void moe_gather_rows_kernel(const uint8_t* __restrict__ a, int64_t lda_bytes, int row_bytes, const int* __restrict__ sorted_ids,
+                                       int64_t capacity, int num_valid, int div, uint8_t* __restrict__ out, int64_t ldo_bytes) {
+  const int per_row = row_bytes / 16;
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= capacity * per_row) return;
+  const int64_t r = i / per_row;
+  const int c = static_cast<int>(i - r * per_row);
+  const int id = sorted_ids[r];
+  uint4 v = make_uint4(0u, 0u, 0u, 0u);
+  if (id < num_valid) v = *reinterpret_cast<const uint4*>(a + static_cast<int64_t>(id / div) * lda_bytes + c * 16);
+  *reinterpret_cast<uint4*>(out + r * ldo_bytes + c * 16) = v;
 }
 
 }  // namespace hm

@@ -262,48 +262,84 @@ __global__ void dequant_prepared_mxfp4_kernel(const uint8_t* __restrict__ w, con
 }
 
 // ---- MoE block alignment (humming/utils/test.py:154-183 does this in a Python loop) ----
-// counts[e] = number of flat (token, slot) entries routed to expert e.
-__global__ void moe_count_kernel(const int* __restrict__ topk_ids, int numel, int num_experts, int* __restrict__ counts) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+// The flat (token, slot) entries are cut into chunks of 1024; three launches:
+//   1. per chunk, a histogram over the experts (also fills sorted_ids with the sentinel),
+//   2. one CTA turns the histograms into, per chunk and expert, the position of the
+//      chunk's first entry inside the expert's (block-padded) range, and writes
+//      expert_ids / num_post_padded,
+//   3. per chunk, every entry is placed: entries of one expert keep ascending flat id.
+constexpr int kAlignChunk = 1024;
+constexpr int kAlignMaxExperts = 1024;  // histogram in shared memory, one thread per expert in step 2
+
+__global__ void __launch_bounds__(kAlignChunk) moe_align_hist_kernel(const int* __restrict__ topk_ids, int numel, int num_experts,
+                                                                     int capacity, int* __restrict__ chunk_pos,
+                                                                     int* __restrict__ sorted_ids) {
+  __shared__ int hist[kAlignMaxExperts];
+  for (int e = threadIdx.x; e < num_experts; e += blockDim.x) hist[e] = 0;
+  __syncthreads();
+  const int i = blockIdx.x * kAlignChunk + threadIdx.x;
   if (i < numel) {
     const int e = topk_ids[i];
-    if (e >= 0 && e < num_experts) atomicAdd(&counts[e], 1);
-  }
-}
-// One CTA: padded offsets per expert, expert id per block, total padded length;
-// fills sorted_ids with the sentinel `numel`.
-__global__ void moe_scan_kernel(const int* __restrict__ counts, int num_experts, int block, int numel, int capacity,
-                                int* __restrict__ offsets, int* __restrict__ expert_ids, int* __restrict__ num_post_padded,
-                                int* __restrict__ sorted_ids) {
-  __shared__ int total;
-  if (threadIdx.x == 0) {
-    int off = 0;
-    for (int e = 0; e < num_experts; ++e) {
-      offsets[e] = off;
-      const int nblk = (counts[e] + block - 1) / block;
-      for (int b = 0; b < nblk; ++b) expert_ids[off / block + b] = e;
-      off += nblk * block;
-    }
-    total = off;
-    *num_post_padded = off;
+    if (e >= 0 && e < num_experts) atomicAdd(&hist[e], 1);
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < capacity; i += blockDim.x) sorted_ids[i] = numel;
-  (void)total;
+  for (int e = threadIdx.x; e < num_experts; e += blockDim.x) chunk_pos[blockIdx.x * num_experts + e] = hist[e];
+  for (int j = blockIdx.x * kAlignChunk + threadIdx.x; j < capacity; j += gridDim.x * kAlignChunk) sorted_ids[j] = numel;
 }
-// One warp per expert: stable compaction (ascending flat id) of its entries.
-__global__ void moe_scatter_kernel(const int* __restrict__ topk_ids, int numel, int num_experts,
-                                   const int* __restrict__ offsets, int* __restrict__ sorted_ids) {
-  const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (e >= num_experts) return;
-  int pos = offsets[e];
-  for (int base = 0; base < numel; base += 32) {
-    const int i = base + lane;
-    const bool hit = i < numel && topk_ids[i] == e;
-    const unsigned mask = __ballot_sync(0xffffffffu, hit);
-    if (hit) sorted_ids[pos + __popc(mask & ((1u << lane) - 1u))] = i;
-    pos += __popc(mask);
+
+// One CTA of 1024 threads, thread e = expert e.
+__global__ void __launch_bounds__(1024) moe_align_scan_kernel(int* __restrict__ chunk_pos, int chunks, int num_experts, int block,
+                                                              int* __restrict__ expert_ids, int* __restrict__ num_post_padded) {
+  __shared__ int scan[1024];
+  const int e = threadIdx.x;
+  int count = 0;
+  if (e < num_experts) {
+    for (int c = 0; c < chunks; ++c) {  // exclusive prefix over the chunks, in place
+      const int v = chunk_pos[c * num_experts + e];
+      chunk_pos[c * num_experts + e] = count;
+      count += v;
+    }
+  }
+  const int padded = (count + block - 1) / block * block;
+  scan[e] = padded;
+  __syncthreads();
+  for (int d = 1; d < 1024; d <<= 1) {  // inclusive scan over the experts
+    const int v = e >= d ? scan[e - d] : 0;
+    __syncthreads();
+    scan[e] += v;
+    __syncthreads();
+  }
+  const int offset = scan[e] - padded;
+  if (e < num_experts) {
+    for (int c = 0; c < chunks; ++c) chunk_pos[c * num_experts + e] += offset;
+    for (int b = 0; b < padded / block; ++b) expert_ids[offset / block + b] = e;
+  }
+  if (e == 1023) *num_post_padded = scan[e];
+}
+
+__global__ void __launch_bounds__(kAlignChunk) moe_align_place_kernel(const int* __restrict__ topk_ids, int numel, int num_experts,
+                                                                      const int* __restrict__ chunk_pos, int* __restrict__ sorted_ids) {
+  __shared__ int next[kAlignMaxExperts];  // next free position of each expert for this chunk
+  for (int e = threadIdx.x; e < num_experts; e += blockDim.x) next[e] = chunk_pos[blockIdx.x * num_experts + e];
+  __syncthreads();
+  const int i = blockIdx.x * kAlignChunk + threadIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int e = -1;
+  if (i < numel) {
+    e = topk_ids[i];
+    if (e < 0 || e >= num_experts) e = -1;
+  }
+  // Lanes of a warp holding the same expert, in lane order; the warps take turns in order.
+  const unsigned same = __match_any_sync(0xffffffffu, e);
+  const int rank = __popc(same & ((1u << lane) - 1u));
+  for (int w = 0; w < kAlignChunk / 32; ++w) {
+    if (w == warp && e >= 0) {
+      const int base = next[e];
+      sorted_ids[base + rank] = i;
+      __syncwarp(same);
+      if (rank == 0) next[e] = base + __popc(same);
+    }
+    __syncthreads();
   }
 }
 

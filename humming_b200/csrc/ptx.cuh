@@ -187,6 +187,12 @@ HM_DEVICE void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
 HM_DEVICE void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// The barrier receives one arrival (already counted in its expected count) once all
+// cp.async copies this thread has issued so far have landed.
+HM_DEVICE void cp_async_mbar_arrive_noinc(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+HM_DEVICE void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 template <int N>
 HM_DEVICE void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");

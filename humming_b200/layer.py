@@ -15,6 +15,8 @@ Differences a caller can observe:
 import dataclasses
 from typing import Optional
 
+import math
+
 import torch
 
 from humming_b200 import dtypes
@@ -375,7 +377,8 @@ class HummingMethod(torch.nn.Module):
     def forward_layer(cls, layer, inputs: torch.Tensor, outputs: Optional[torch.Tensor] = None,
                       input_scale: Optional[torch.Tensor] = None, topk_weights: Optional[torch.Tensor] = None,
                       sorted_token_ids: Optional[torch.Tensor] = None, expert_ids: Optional[torch.Tensor] = None,
-                      num_tokens_post_padded: Optional[torch.Tensor] = None, sublayer_name: str = ""):
+                      num_tokens_post_padded: Optional[torch.Tensor] = None, sublayer_name: str = "",
+                      inputs_sorted: bool = False, outputs_sorted: bool = False, num_tokens: Optional[int] = None):
         """``C = A . dequant(W)^T (+ bias)`` on the current stream
         (``humming/layer.py:519-550``).  Asynchronous; concurrent forwards of the
         same layer on different streams share one workspace and are not supported
@@ -385,7 +388,7 @@ class HummingMethod(torch.nn.Module):
             raise RuntimeError("call finish_load before forward")
         if meta.num_experts is not None:
             return cls._forward_moe(layer, meta, inputs, outputs, input_scale, topk_weights, sorted_token_ids, expert_ids,
-                                    num_tokens_post_padded, sublayer_name)
+                                    num_tokens_post_padded, sublayer_name, inputs_sorted, outputs_sorted, num_tokens)
         if sorted_token_ids is not None:
             raise ValueError("routing tensors given to a dense layer")
         if meta.a_dtype.num_bits != 16 and inputs.dtype in _FLOAT_DTYPES:
@@ -441,11 +444,17 @@ class HummingMethod(torch.nn.Module):
 
     @classmethod
     def _forward_moe(cls, layer, meta, inputs, outputs, input_scale, topk_weights, sorted_token_ids, expert_ids,
-                     num_tokens_post_padded, sublayer_name):
+                     num_tokens_post_padded, sublayer_name, inputs_sorted=False, outputs_sorted=False, num_tokens=None):
         """Indexed GEMM over the experts (reference docs/CONFIG.md "MoE Config"):
         up projection reads row ``id // top_k`` of ``inputs (M, K)``, down projection row
         ``id`` of ``inputs (M, top_k, K)`` and multiplies by ``topk_weights``; both write
-        row ``id`` of ``outputs (M, top_k, N)``."""
+        row ``id`` of ``outputs (M, top_k, N)``.
+
+        Extensions without a counterpart in the reference: ``inputs_sorted`` -- ``inputs`` is
+        ``(len(sorted_token_ids), K)``, row i belonging to entry ``sorted_token_ids[i]`` (see
+        ``runtime.moe_gather_rows``), loaded as tiles instead of gathered row by row, and
+        ``num_tokens`` must be given; ``outputs_sorted`` -- the result is
+        ``(len(sorted_token_ids), N)`` in the same order instead of scattered by id."""
         opts = layer.humming_kernel_options[sublayer_name]
         top_k = opts.get("top_k", 0)
         is_down = bool(opts.get("is_moe_down", False))
@@ -455,7 +464,12 @@ class HummingMethod(torch.nn.Module):
             raise ValueError("MoE forward needs sorted_token_ids, expert_ids and num_tokens_post_padded")
         if is_down and topk_weights is None:
             raise ValueError("the down projection needs topk_weights")
-        num_tokens = inputs.size(0)
+        if inputs_sorted:
+            if num_tokens is None:
+                raise ValueError("inputs_sorted needs num_tokens")
+        else:
+            num_tokens = inputs.size(0)
+        capacity = sorted_token_ids.numel()
         if meta.a_dtype.num_bits != 16 and inputs.dtype in _FLOAT_DTYPES:
             input_scale = None
         inputs, input_scale = cls.may_quant_input(meta, inputs, input_scale)
@@ -466,7 +480,7 @@ class HummingMethod(torch.nn.Module):
             input_scale = input_scale.reshape(-1).float().contiguous()
             if input_scale.numel() != a.size(0):
                 raise ValueError("input_scale must hold one fp32 scale per activation row")
-        if a.size(1) != meta.shape_k or a.size(0) != num_tokens * (top_k if is_down else 1):
+        if a.size(1) != meta.shape_k or a.size(0) != (capacity if inputs_sorted else num_tokens * (top_k if is_down else 1)):
             raise ValueError(f"inputs of shape {tuple(inputs.shape)} do not fit a "
                              f"{'down' if is_down else 'up'} projection with K={meta.shape_k}, top_k={top_k}")
         if a.dtype != dtypes.torch_dtype_map[meta.a_dtype]:
@@ -475,13 +489,15 @@ class HummingMethod(torch.nn.Module):
         if sorted_token_ids.numel() % block:
             raise ValueError(f"sorted_token_ids must be aligned to blocks of {block} for {num_tokens} tokens")
         c_dtype = dtypes.torch_dtype_map[meta.c_dtype]
+        out_shape = (capacity, meta.shape_n) if outputs_sorted else (num_tokens, top_k, meta.shape_n)
         if outputs is None:
-            outputs = torch.empty((num_tokens, top_k, meta.shape_n), dtype=c_dtype, device=a.device)
+            outputs = torch.empty(out_shape, dtype=c_dtype, device=a.device)
         else:
-            assert outputs.dtype == c_dtype and outputs.is_contiguous() and outputs.numel() == num_tokens * top_k * meta.shape_n
+            assert outputs.dtype == c_dtype and outputs.is_contiguous() and outputs.numel() == out_shape[0] * math.prod(out_shape[1:])
         if num_tokens == 0:
             return outputs
-        desc = cls._desc(meta, m_tile=block, top_k=top_k, is_moe_down=is_down)
+        flags = (native.HM_FLAG_MOE_A_SORTED if inputs_sorted else 0) | (native.HM_FLAG_MOE_C_SORTED if outputs_sorted else 0)
+        desc = cls._desc(meta, m_tile=block, top_k=top_k, is_moe_down=is_down, flags=flags)
         ws = cls._workspace(layer, runtime.moe_workspace_bytes(desc, sorted_token_ids.numel()), a.device)
         ids = sorted_token_ids if sorted_token_ids.dtype == torch.int32 else sorted_token_ids.int()
         tkw = None if topk_weights is None else topk_weights.reshape(-1).float().contiguous()

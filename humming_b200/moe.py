@@ -127,17 +127,19 @@ class HummingMoE(torch.nn.Module):
             return rows.new_empty((0, self.hidden_size))
         block = HummingMethod.moe_block_size(self.up, tokens)
         sorted_ids, expert_ids, total = runtime.moe_align_block_size(local_e, self.ep.experts_per_rank, block)
-        routing = dict(sorted_token_ids=sorted_ids, expert_ids=expert_ids, num_tokens_post_padded=total)
+        routing = dict(sorted_token_ids=sorted_ids, expert_ids=expert_ids, num_tokens_post_padded=total, num_tokens=tokens)
+        # Activations are brought into the order of sorted_ids once and stay in it between the two
+        # GEMMs (tiled loads instead of row gathers); only the down projection scatters by id.
+        rows_sorted = runtime.moe_gather_rows(rows, sorted_ids, tokens * top_k, top_k)
+        rows_scale = None
         if self.fp8:
-            rows, rows_scale = runtime.quant_input(rows, "float8e4m3")
-            h = self.up(inputs=rows, input_scale=rows_scale, **routing)        # (T, k, 2I)
-        else:
-            h = self.up(inputs=rows, **routing)
-        act = runtime.silu_mul(h.view(tokens * top_k, 2 * self.intermediate_size))
+            rows_sorted, rows_scale = runtime.quant_input(rows_sorted, "float8e4m3")
+        h = self.up(inputs=rows_sorted, input_scale=rows_scale, inputs_sorted=True, outputs_sorted=True, **routing)  # (capacity, 2I)
+        act = runtime.silu_mul(h)
         act_scale = None
         if self.fp8:
             act, act_scale = runtime.quant_input(act, "float8e4m3")
-        out = self.down(inputs=act.view(tokens, top_k, self.intermediate_size), input_scale=act_scale, topk_weights=w, **routing)
+        out = self.down(inputs=act, input_scale=act_scale, topk_weights=w, inputs_sorted=True, **routing)  # (T, k, H)
         return out.view(tokens * top_k, self.hidden_size)
 
     def forward(self, hidden_states: torch.Tensor, router_logits: torch.Tensor) -> torch.Tensor:

@@ -22,6 +22,8 @@ HM_FLAG_A_OPERAND_SMEM = 1
 HM_FLAG_NO_SPLIT_K = 2
 HM_FLAG_CTA_PAIR = 4
 HM_FLAG_NO_CTA_PAIR = 8
+HM_FLAG_MOE_A_SORTED = 16
+HM_FLAG_MOE_C_SORTED = 32
 
 
 class GemmDesc(ctypes.Structure):
@@ -58,8 +60,10 @@ SIGNATURES = {
     "hm_gemm_workspace_bytes": (ctypes.c_size_t, [_DESC, _L]),
     "hm_gemm": (_I, [_DESC, _L, _P, _L, _P, _P, _P, _P, _P, _P, _L, _P, ctypes.c_size_t, _P]),
     "hm_moe_align_block_size": (_I, [_P, _L, _I, _I, _P, _L, _P, _P, _P, _P]),
+    "hm_moe_align_scratch_ints": (_L, [_L, _I]),
     "hm_moe_gemm_workspace_bytes": (ctypes.c_size_t, [_DESC, _L]),
     "hm_moe_gemm": (_I, [_DESC, _L, _P, _L, _P, _P, _P, _P, _P, _P, _P, _L, _P, _P, _P, _L, _P, ctypes.c_size_t, _P]),
+    "hm_moe_gather_rows": (_I, [_P, _L, _L, _P, _L, _L, _I, _P, _L, _P]),
     "hm_moe_route": (_I, [_P, _L, _I, _I, _I, _I, _P, _P, _P]),
     "hm_silu_mul": (_I, [_P, _P, _L, _I, _I, _P]),
     "hm_topk_sum": (_I, [_P, _P, _L, _I, _I, _I, _P]),

@@ -162,11 +162,23 @@ def moe_align_block_size(topk_ids: torch.Tensor, num_experts: int, block: int):
     sorted_ids = torch.empty(capacity, dtype=torch.int32, device=dev)
     expert_ids = torch.empty(capacity // block, dtype=torch.int32, device=dev)
     total = torch.empty(1, dtype=torch.int32, device=dev)
-    scratch = torch.empty(2 * num_experts, dtype=torch.int32, device=dev)
+    scratch = torch.empty(native.lib.hm_moe_align_scratch_ints(numel, num_experts), dtype=torch.int32, device=dev)
     with torch.cuda.device(dev):
         native.check(native.lib.hm_moe_align_block_size(_ptr(ids), numel, num_experts, block, _ptr(sorted_ids), capacity,
                                                         _ptr(expert_ids), _ptr(total), _ptr(scratch), _stream(dev)))
     return sorted_ids, expert_ids, total
+
+
+def moe_gather_rows(a: torch.Tensor, sorted_ids: torch.Tensor, num_valid: int, div: int) -> torch.Tensor:
+    """a (rows, width) -> (len(sorted_ids), width): row i = a[sorted_ids[i] // div], zeros for padding entries."""
+    _require_cuda(a, sorted_ids)
+    assert a.dim() == 2 and a.stride(1) == 1 and sorted_ids.dtype == torch.int32 and sorted_ids.is_contiguous()
+    out = torch.empty((sorted_ids.numel(), a.size(1)), dtype=a.dtype, device=a.device)
+    es = a.element_size()
+    with torch.cuda.device(a.device):
+        native.check(native.lib.hm_moe_gather_rows(_ptr(a), a.stride(0) * es, a.size(1) * es, _ptr(sorted_ids), sorted_ids.numel(),
+                                                   num_valid, div, _ptr(out), out.stride(0) * es, _stream(a.device)))
+    return out
 
 
 def moe_workspace_bytes(desc: native.GemmDesc, capacity: int) -> int:

@@ -85,6 +85,16 @@ typedef struct hm_gemm_desc {
  * plan decides.  No counterpart in the reference (one CTA per tile there). */
 #define HM_FLAG_CTA_PAIR 4
 #define HM_FLAG_NO_CTA_PAIR 8
+/* hm_moe_gemm only.  A_SORTED: `a` holds one row per entry of sorted_ids, in that
+ * order (`capacity` rows, as hm_moe_gather_rows writes them; a_scale likewise one
+ * per sorted row), so activation tiles are loaded by TMA instead of gathered row by
+ * row.  C_SORTED: `c` receives one row per entry of sorted_ids, in that order
+ * (`capacity` rows, padding rows included), instead of being scattered by id.
+ * A layer that keeps its intermediate activations in sorted order gathers once
+ * (up projection input) and scatters once (down projection output).  No
+ * counterpart in the reference, whose kernel always gathers and scatters. */
+#define HM_FLAG_MOE_A_SORTED 16
+#define HM_FLAG_MOE_C_SORTED 32
 
 /* Launch plan chosen for (desc, m); returned by hm_gemm_plan for tests,
  * benchmarks and workspace sizing. */
@@ -173,12 +183,25 @@ HM_API int hm_gemm(const hm_gemm_desc* desc, int64_t m, const void* a, int64_t l
  * expert, ascending id inside an expert, each expert padded to a multiple of
  * `block` with the sentinel `numel`: sorted_ids[capacity] (capacity >=
  * numel + num_experts * (block - 1), rounded up to a multiple of block),
- * expert_ids[capacity / block], num_post_padded[1].  scratch: 2 * num_experts
- * ints.  The reference leaves this to the caller and does it in a Python loop
- * (humming/utils/test.py:154-183, "TODO: moe_align_block_size cuda kernel"). */
+ * expert_ids[capacity / block], num_post_padded[1].  scratch:
+ * hm_moe_align_scratch_ints(numel, num_experts) ints (one histogram per 1024
+ * entries); at most 1024 experts.  The reference leaves this to the caller and
+ * does it in a Python loop (humming/utils/test.py:154-183, "TODO:
+ * moe_align_block_size cuda kernel"). */
 HM_API int hm_moe_align_block_size(const int32_t* topk_ids, int64_t numel, int num_experts, int block,
                                    int32_t* sorted_ids, int64_t capacity, int32_t* expert_ids,
                                    int32_t* num_post_padded, int32_t* scratch, void* stream);
+/* Number of int32 of scratch hm_moe_align_block_size needs (0 for bad arguments). */
+HM_API int64_t hm_moe_align_scratch_ints(int64_t numel, int num_experts);
+
+/* out[i, :] = a[sorted_ids[i] / div, :] for i < capacity (zeros where sorted_ids[i] >=
+ * num_valid): brings activation rows into the order of sorted_ids for
+ * HM_FLAG_MOE_A_SORTED.  div = top_k when `a` has one row per token, 1 when it has one
+ * row per (token, slot).  Row lengths and pitches in bytes, multiples of 16.  The
+ * reference has no such step (its kernel gathers,
+ * humming/include/humming/memory/g2s_loader/loader_a.cuh:76-91). */
+HM_API int hm_moe_gather_rows(const void* a, int64_t lda_bytes, int64_t row_bytes, const int32_t* sorted_ids, int64_t capacity,
+                              int64_t num_valid, int div, void* out, int64_t ldo_bytes, void* stream);
 
 /* Workspace bytes of hm_moe_gemm for a sorted_ids buffer of `capacity` entries
  * (desc->m_tile = block size used for the alignment: 16, 32, 64 or 128). */

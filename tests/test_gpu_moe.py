@@ -96,3 +96,32 @@ def test_qwen3_moe_shapes(cuda_device, tokens, proj):
     out2 = layer(inputs=inputs.to(cuda_device), topk_weights=topk_weights.to(cuda_device), sorted_token_ids=sorted_ids,
                  expert_ids=expert_ids, num_tokens_post_padded=total)
     assert torch.equal(out, out2)
+
+
+@pytest.mark.parametrize("m", [1, 18, 512, 3000])
+@pytest.mark.parametrize("is_down", [True, False])
+def test_moe_gemm_sorted_inputs_and_outputs(cuda_device, m, is_down):
+    """Activations pre-gathered into the order of sorted_token_ids and outputs left in
+    that order give exactly the rows the gathering / scattering kernel produces."""
+    dtype, e, top_k = torch.bfloat16, 8, 2
+    layer, _ = make_moe_layer(e, 512, 1024, dtype, True, cuda_device, top_k, is_down, seed=m + 1)
+    gen = torch.Generator(device="cpu").manual_seed(9)
+    logits = torch.randn((m, e), generator=gen)
+    topk_weights, topk_ids = logits.topk(top_k, 1)
+    x = torch.randn((m * (top_k if is_down else 1), 1024), generator=gen).to(dtype).to(cuda_device)
+    block = HummingMethod.moe_block_size(layer, m)
+    sorted_ids, expert_ids, total = runtime.moe_align_block_size(topk_ids.int().to(cuda_device), e, block)
+    routing = dict(topk_weights=topk_weights.to(cuda_device), sorted_token_ids=sorted_ids, expert_ids=expert_ids,
+                   num_tokens_post_padded=total)
+    want = layer(inputs=x.view(m, top_k, -1) if is_down else x, **routing).view(m * top_k, 512)
+    xs = runtime.moe_gather_rows(x, sorted_ids, m * top_k, 1 if is_down else top_k)
+    t = int(total.item())
+    ids = sorted_ids[:t].long()
+    real = ids < m * top_k
+    assert torch.equal(xs[:t][real], x[ids[real] // (1 if is_down else top_k)]) and not bool(xs[:t][~real].any())
+    got_scattered = layer(inputs=xs, inputs_sorted=True, num_tokens=m, **routing).view(m * top_k, 512)
+    got_sorted = layer(inputs=xs, inputs_sorted=True, outputs_sorted=True, num_tokens=m, **routing)
+    layer.check_status()
+    assert got_sorted.shape == (sorted_ids.numel(), 512)
+    assert torch.equal(got_scattered, want)
+    assert torch.equal(got_sorted[:t][real], want[ids[real]])

@@ -167,6 +167,11 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+# DRAM bytes per launch from the ncu captures summarised under profiles/ (read + write).
+NCU_DRAM_BYTES_GATE_UP_4096 = 1.044e9   # profiles/gemm_w4a16_gate_up_m4096_prefill.md (algorithmic: 0.329e9)
+NCU_DRAM_BYTES_GATE_UP_16 = 61.5e6      # profiles/gemm_w4a16_gate_up_m16_decode.md
+
+
 def run_point(args):
     """`--point PROJ:M`: a few eager launches of one sweep point (used for ncu captures)."""
     from humming_b200.layer import HummingLayer
@@ -420,11 +425,12 @@ def run_ours(args, rank, world, local_rank):
         "gpu_launches": len(points) * args.steps,
         "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": big_ach, "peak": peak_tc, "unit": "TFLOP/s", "frac": big_ach / peak_tc,
-                     "traffic": None, "kernel": "gemm_w4a16_kernel<256,bf16,zp,tmem>, CTA-pair or single-CTA instantiation as planned "
+                     "traffic": NCU_DRAM_BYTES_GATE_UP_4096, "traffic_note": "ncu dram read+write bytes of the gate_up M=4096 launch", "kernel": "gemm_w4a16_kernel<256,bf16,zp,tmem>, CTA-pair or single-CTA instantiation as planned "
                                f"({sum(p['cta_pair'] for p in big)} of {len(big)} launches on the 256-token tile are CTA pairs)",
                      "peak_source": f"{peaks['source']} cuBLAS bf16, sustained", "top_launch": top},
         "roofline_decode": {"bound": "hbm", "achieved": small_ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                            "frac": small_ach / peaks["hbm_gbs"], "traffic": None,
+                            "frac": small_ach / peaks["hbm_gbs"], "traffic": NCU_DRAM_BYTES_GATE_UP_16,
+                            "traffic_note": "ncu dram read+write bytes of the gate_up M=16 launch (algorithmic: 62.06 MB)",
                             "kernel": "gemm_w4a16_kernel<16,bf16,zp,tmem> (all launches with M <= 16)",
                             "peak_source": f"{peaks['source']} copy bandwidth"},
         "cpu_baseline": cpu,

@@ -235,13 +235,21 @@ def run_moe(args, rank, world, local_rank):
         for _ in range(max(args.warmup, 3)):
             moe(x, logits)
         moe.check_status()
+        step = lambda: moe(x, logits)
+        if world == 1:
+            # One GPU: no host-side step in the layer, so a forward is captured once and replayed.
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                moe(x, logits)
+            step = graph.replay
+            step()
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(args.steps):
-            moe(x, logits)
+            step()
         e1.record()
         if world > 1:
             dist.barrier()
@@ -261,9 +269,94 @@ def run_moe(args, rank, world, local_rank):
         "config": {"workload": "qwen3-30b-a3b MoE layer: route, align, up GEMM, silu*mul, down GEMM, top-k sum",
                    "experts": experts, "top_k": top_k, "hidden": hidden, "intermediate": inter, "tokens_total": top["tokens"],
                    "parallelism": f"ep{world}" if world > 1 else "single GPU",
-                   "timing": "eager, CUDA events, max over ranks (the exchange sizes are read on the host)"},
+                   "timing": "one GPU: CUDA graph of a forward replayed K times; expert parallel: eager (the exchange sizes are read on the host); "
+                             "CUDA events, max over ranks"},
         "tflops": top["tokens_per_s"] * flops_per_token / 1e12,
         "sweep": results,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_mxfp4(args):
+    """`--workload mxfp4`: BASELINE.json configs[2], MXFP4 x FP8 dense GEMM, N = K = 8192, M sweep 1..8192:
+    FP4 e2m1 codes with UE8M0 scales per 32 K-elements (exponents uniform in [-8, -2]), e4m3 activations with a
+    per-token fp32 scale = amax / 448 (quantized beforehand, outside the timed region), bf16 output.  One GPU."""
+    from humming_b200 import runtime
+    from humming_b200.layer import HummingLayer
+
+    dev = torch.device("cuda", 0)
+    n = k = 8192
+    m_sweep = (1, 16, 64, 256, 1024, 4096, 8192)
+    gen = torch.Generator(device=dev).manual_seed(0)
+    layers = []
+    for _ in range(N_COPIES):  # 3 x 36 MB of weights: rotated, loaded evict-first
+        codes = torch.randint(0, 16, (n, k), generator=gen, dtype=torch.int32, device=dev)
+        scales = (torch.randint(-8, -1, (n, k // 32), generator=gen, device=dev) + 127).to(torch.uint8).view(torch.float8_e8m0fnu)
+        layer = HummingLayer(shape_n=n, shape_k=k, a_dtype="float8e4m3", b_dtype="float4e2m1", c_dtype="bfloat16",
+                             bs_dtype="float8e8m0", weight_scale_group_size=32).to(dev)
+        layer.load_weight(weight=codes, weight_scale=scales)
+        layer.finish_load()
+        layers.append(layer)
+        del codes, scales
+    acts = {}
+    for m in m_sweep:
+        x = torch.randn((m, k), generator=gen, device=dev).bfloat16()
+        acts[m] = runtime.quant_input(x, "float8e4m3")
+    outs = {m: torch.empty((m, n), dtype=torch.bfloat16, device=dev) for m in m_sweep}
+
+    def one_step():
+        for mi, m in enumerate(m_sweep):
+            q, sc = acts[m]
+            layers[mi % N_COPIES](inputs=q, input_scale=sc, outputs=outs[m])
+
+    for _ in range(max(args.warmup, 3)):
+        one_step()
+    for layer in layers:
+        layer.check_status()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        one_step()
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    per_point = []
+    for mi, m in enumerate(m_sweep):
+        q, sc = acts[m]
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for r in range(6):
+                layers[r % N_COPIES](inputs=q, input_scale=sc, outputs=outs[m])
+        g.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(3):
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) * 1e3 / 18
+        bytes_ = n * k / 2 + n * (k // 32) + m * k + m * 4 + m * n * 2
+        per_point.append({"m": m, "us": round(us, 2), "tflops": round(2.0 * m * n * k / us / 1e6, 2), "gbs": round(bytes_ / us / 1e3, 1)})
+        del g
+    flops = sum(2.0 * m * n * k for m in m_sweep)
+    line = {
+        "metric": "MXFP4 x FP8 dense GEMM throughput, N = K = 8192, M sweep (e2m1 weights + UE8M0/32, e4m3 activations)",
+        "value": flops / (ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 tensor path after exact widening of e2m1 x UE8M0 weights and e4m3 activations; fp32 accumulation",
+        "data": "synthetic",
+        "config": {"workload": "mxfp4 x fp8 dense, 7 GEMMs per step", "shape_nk": [n, k], "m_sweep": list(m_sweep),
+                   "l2": f"{N_COPIES} rotating weight copies, weights loaded evict-first",
+                   "timing": "CUDA graph of one step replayed K times, CUDA events; activation quantization outside the timed region, "
+                             "the exact e4m3 -> bf16 widening of the activations inside"},
+        "gpu_launches": 2 * len(m_sweep) * args.steps,
+        "sweep": per_point,
     }
     print(json.dumps(line), flush=True)
 
@@ -446,8 +539,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="dense", choices=["dense", "moe"])
-    ap.add_argument("--tokens", default="32,512,4096", help="moe workload: total token counts to time, the last one is the headline")
+    ap.add_argument("--workload", default="dense", choices=["dense", "moe", "mxfp4"])
+    ap.add_argument("--tokens", default="1,32,512,4096", help="moe workload: total token counts to time, the last one is the headline")
     ap.add_argument("--native-flags", type=int, default=0, help="HM_FLAG_* bits OR-ed into every dense GEMM descriptor (kernel A/B comparisons)")
     ap.add_argument("--point", default=None, help="PROJ:M, e.g. gate_up:16 -- launch only this sweep point a few times")
     args = ap.parse_args()
@@ -457,6 +550,9 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.workload == "mxfp4" and args.impl == "ours":
+        run_mxfp4(args)
         return
     if args.point:
         run_point(args)

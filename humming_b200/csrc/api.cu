@@ -163,7 +163,7 @@ int make_plan(const hm_gemm_desc* d, int64_t m, hm_plan* plan) {
   if (smem_operand && d->m_tile > 128)
     return fail(HM_ERR_UNSUPPORTED, "the shared-memory operand variant is built for token tiles up to 128");
   // CTA pairs (cta_group::2): 256 weight rows per tile, token tile a multiple of 32.
-  const bool pair_ok = !smem_operand && d->b_dtype != HM_E2M1 && d->shape_n % (2 * hm::kTileN) == 0 && !(d->flags & HM_FLAG_NO_CTA_PAIR);
+  const bool pair_ok = !smem_operand && d->shape_n % (2 * hm::kTileN) == 0 && !(d->flags & HM_FLAG_NO_CTA_PAIR);
   const bool pair_forced = pair_ok && (d->flags & HM_FLAG_CTA_PAIR);
   const int kb = d->shape_k / hm::kStageK;
 
@@ -278,10 +278,10 @@ int launch_gemm(const hm::GemmParams& p, const CUtensorMap& tmap, int grid, cuda
 }
 
 // CTA-pair kernel: `pairs` clusters of two CTAs.
-template <int MT, bool BF16, bool HAS_ZP>
+template <int MT, bool BF16, bool HAS_ZP, int WFMT = 0>
 int launch_gemm_pair(const hm::GemmParams& p, const CUtensorMap& tmap, int pairs, cudaStream_t stream) {
   using Cfg = hm::GemmCfg<MT, true, true>;
-  auto kern = hm::gemm_w4a16_kernel<MT, BF16, HAS_ZP, true, false, 0, true>;
+  auto kern = hm::gemm_w4a16_kernel<MT, BF16, HAS_ZP, true, false, WFMT, true>;
   static bool configured[64] = {false};
   int dev = 0;
   HM_CUDA_OK(cudaGetDevice(&dev));
@@ -308,7 +308,8 @@ int launch_gemm_pair(const hm::GemmParams& p, const CUtensorMap& tmap, int pairs
 }
 
 template <int MT>
-int dispatch_gemm_pair(bool bf16, bool zp, const hm::GemmParams& p, const CUtensorMap& tmap, int pairs, cudaStream_t stream) {
+int dispatch_gemm_pair(bool bf16, bool zp, int wfmt, const hm::GemmParams& p, const CUtensorMap& tmap, int pairs, cudaStream_t stream) {
+  if (wfmt == 1) return launch_gemm_pair<MT, true, false, 1>(p, tmap, pairs, stream);
   if (bf16) return zp ? launch_gemm_pair<MT, true, true>(p, tmap, pairs, stream) : launch_gemm_pair<MT, true, false>(p, tmap, pairs, stream);
   return zp ? launch_gemm_pair<MT, false, true>(p, tmap, pairs, stream) : launch_gemm_pair<MT, false, false>(p, tmap, pairs, stream);
 }
@@ -581,10 +582,10 @@ int hm_gemm(const hm_gemm_desc* desc, int64_t m, const void* a, int64_t lda, con
   auto s = static_cast<cudaStream_t>(stream);
   if (pl.cta_pair) {
     switch (pl.m_tile) {
-      case 32: return dispatch_gemm_pair<32>(bf16, desc->has_zp != 0, p, tmap, pl.grid, s);
-      case 64: return dispatch_gemm_pair<64>(bf16, desc->has_zp != 0, p, tmap, pl.grid, s);
-      case 128: return dispatch_gemm_pair<128>(bf16, desc->has_zp != 0, p, tmap, pl.grid, s);
-      case 256: return dispatch_gemm_pair<256>(bf16, desc->has_zp != 0, p, tmap, pl.grid, s);
+      case 32: return dispatch_gemm_pair<32>(bf16, desc->has_zp != 0, wfmt, p, tmap, pl.grid, s);
+      case 64: return dispatch_gemm_pair<64>(bf16, desc->has_zp != 0, wfmt, p, tmap, pl.grid, s);
+      case 128: return dispatch_gemm_pair<128>(bf16, desc->has_zp != 0, wfmt, p, tmap, pl.grid, s);
+      case 256: return dispatch_gemm_pair<256>(bf16, desc->has_zp != 0, wfmt, p, tmap, pl.grid, s);
     }
     return fail(HM_ERR_INVALID, "no CTA-pair kernel for m_tile=%d", pl.m_tile);
   }

@@ -79,7 +79,7 @@ typedef struct hm_gemm_desc {
 #define HM_FLAG_NO_SPLIT_K 2
 /* Dense GEMM on clusters of two CTAs sharing one 256-row weight tile
  * (tcgen05 cta_group::2: half the MMA instructions per SM, each CTA loads half
- * of the activation tile).  Needs shape_n % 256 == 0, integer 4-bit weights and
+ * of the activation tile).  Needs shape_n % 256 == 0 and
  * a token tile of 32, 64, 128 or 256; otherwise the single-CTA kernel runs.
  * HM_FLAG_CTA_PAIR asks for it, HM_FLAG_NO_CTA_PAIR forbids it; with neither the
  * plan decides.  No counterpart in the reference (one CTA per tile there). */

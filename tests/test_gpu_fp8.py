@@ -61,6 +61,27 @@ def test_mxfp4_fp8_gemm(cuda_device, m):
     torch.testing.assert_close(out2.float().cpu(), ref.float(), atol=ATOL, rtol=RTOL)
 
 
+@pytest.mark.parametrize("m", [40, 300])
+def test_mxfp4_fp8_gemm_cta_pair(cuda_device, m):
+    """The two-CTA kernel gives bit-identical results for MXFP4 weights (no K split)."""
+    from humming_b200 import native
+    n, k = 1024, 2048
+    codes, scales, w_ref = mxfp4_case(n, k, seed=2)
+    layer = HummingLayer(shape_n=n, shape_k=k, a_dtype="float8e4m3", b_dtype="float4e2m1", c_dtype="bfloat16",
+                         bs_dtype="float8e8m0", weight_scale_group_size=32).to(cuda_device)
+    layer.load_weight(weight=codes.to(cuda_device), weight_scale=scales.to(cuda_device))
+    layer.finish_load()
+    _, q, s = quantized_acts(m, k, seed=m)
+    outs = []
+    for flags in (native.HM_FLAG_NO_SPLIT_K | native.HM_FLAG_NO_CTA_PAIR, native.HM_FLAG_NO_SPLIT_K | native.HM_FLAG_CTA_PAIR):
+        layer.humming_kernel_options[""]["native_flags"] = flags
+        outs.append(layer(inputs=q.to(cuda_device), input_scale=s.to(cuda_device)).clone())
+    layer.check_status()
+    ref = oracle.gemm_ref(q.float() * s, w_ref, torch.bfloat16)
+    torch.testing.assert_close(outs[1].float().cpu(), ref.float(), atol=ATOL, rtol=RTOL)
+    assert torch.equal(outs[0], outs[1])
+
+
 @pytest.mark.parametrize("signed", [False, True])
 @pytest.mark.parametrize("m", [7, 64, 400])
 def test_w4a8_gemm(cuda_device, signed, m):

@@ -12,6 +12,7 @@
 #include <mutex>
 
 #include "gemm_w4a16.cuh"
+#include "gemv_w4a16.cuh"
 #include "moe_ops.cuh"
 #include "prep.cuh"
 #include "sched.cuh"
@@ -97,6 +98,12 @@ int validate_desc(const hm_gemm_desc* d) {
   return HM_OK;
 }
 
+// Token counts served by the register-level decode kernel (csrc/gemv_w4a16.cuh) instead of the tcgen05
+// kernel: by default up to 4 (measured faster there on B200, 10-35 %; about equal at 8, slower at 16),
+// up to 16 when HM_FLAG_DECODE_KERNEL asks for it.
+constexpr int kGemvPlanMaxM = 4;
+constexpr int kGemvKernelMaxM = 16;
+
 // One way to run (desc, m): token tile, one CTA or a CTA pair per weight tile,
 // whole tiles or a K split.
 struct PlanChoice {
@@ -162,6 +169,38 @@ int make_plan(const hm_gemm_desc* d, int64_t m, hm_plan* plan) {
   const bool smem_operand = (d->flags & HM_FLAG_A_OPERAND_SMEM) != 0;
   if (smem_operand && d->m_tile > 128)
     return fail(HM_ERR_UNSUPPORTED, "the shared-memory operand variant is built for token tiles up to 128");
+  // Up to 16 tokens: the decode kernel (csrc/gemv_w4a16.cuh), K split over enough CTAs to fill the GPU.
+  if (m >= 1 && m <= ((d->flags & HM_FLAG_DECODE_KERNEL) ? kGemvKernelMaxM : kGemvPlanMaxM) && d->m_tile == 0 &&
+      d->b_dtype != HM_E2M1 && d->a_dtype != HM_E4M3 &&
+      !(d->flags & (HM_FLAG_A_OPERAND_SMEM | HM_FLAG_NO_SPLIT_K | HM_FLAG_CTA_PAIR | HM_FLAG_NO_GEMV))) {
+    memset(plan, 0, sizeof(*plan));
+    const int kb = d->shape_k / hm::kStageK;
+    const int n_tiles = d->shape_n / hm::kTileN;
+    // K steps per CTA: as many waves of four CTAs per SM as needed, each lasting its steps plus
+    // about three steps' worth of start-up and partial-sum traffic; the cheapest count wins.
+    const int max_steps = m <= 8 ? 8 : 4;  // a CTA's activations in shared memory: about 16 KB
+    const int slots = 4 * sms;
+    int steps = 1;
+    int64_t best_cost = -1;
+    for (int cand = 1; cand <= max_steps && cand <= kb; ++cand) {
+      const int64_t ctas = static_cast<int64_t>(n_tiles) * ((kb + cand - 1) / cand);
+      const int64_t waves = (ctas + slots - 1) / slots;
+      const int64_t cost = waves * (cand + 3);
+      if (best_cost < 0 || cost <= best_cost) best_cost = cost, steps = cand;
+    }
+    const int splits = (kb + steps - 1) / steps;
+    plan->m_tile = static_cast<int32_t>(m);
+    plan->n_tiles = n_tiles;
+    plan->m_tiles = 1;
+    plan->kb_per_tile = kb;
+    plan->mode = 2;
+    plan->grid = n_tiles * splits;
+    plan->units_per_cta = steps;
+    plan->total_units = static_cast<int64_t>(n_tiles) * kb;
+    const int64_t counters = ((static_cast<int64_t>(n_tiles) * 4 + 255) / 256) * 256;
+    plan->workspace_bytes = 256 + counters + (splits > 1 ? static_cast<int64_t>(splits) * m * d->shape_n * 4 : 0);
+    return HM_OK;
+  }
   // CTA pairs (cta_group::2): 256 weight rows per tile, token tile a multiple of 32.
   const bool pair_ok = !smem_operand && d->shape_n % (2 * hm::kTileN) == 0 && !(d->flags & HM_FLAG_NO_CTA_PAIR);
   const bool pair_forced = pair_ok && (d->flags & HM_FLAG_CTA_PAIR);
@@ -330,6 +369,30 @@ int dispatch_gemm(bool bf16, bool zp, bool a_tmem, int wfmt, const hm::GemmParam
     return zp ? launch_gemm<MT, false, true, false>(p, tmap, grid, stream) : launch_gemm<MT, false, false, false>(p, tmap, grid, stream);
   }
   return fail(HM_ERR_UNSUPPORTED, "no shared-memory operand kernel for m_tile=%d", MT);
+}
+
+constexpr size_t kGemvMaxSmem = 64 * 1024;
+
+template <int NT, bool BF16, bool HAS_ZP>
+int launch_gemv_one(const hm::GemvParams& p, int grid, size_t smem, cudaStream_t stream) {
+  auto kern = hm::gemv_w4a16_kernel<NT, BF16, HAS_ZP>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  HM_CUDA_OK(cudaGetDevice(&dev));
+  if (!configured[dev & 63]) {
+    HM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemvMaxSmem)));
+    configured[dev & 63] = true;
+  }
+  if (smem > kGemvMaxSmem) return fail(HM_ERR_INVALID, "decode kernel: %zu bytes of shared memory asked for", smem);
+  kern<<<grid, hm::kGemvThreads, smem, stream>>>(p);
+  HM_CUDA_OK(cudaGetLastError());
+  return HM_OK;
+}
+
+template <int NT>
+int launch_gemv(bool bf16, bool zp, const hm::GemvParams& p, int grid, size_t smem, cudaStream_t stream) {
+  if (bf16) return zp ? launch_gemv_one<NT, true, true>(p, grid, smem, stream) : launch_gemv_one<NT, true, false>(p, grid, smem, stream);
+  return zp ? launch_gemv_one<NT, false, true>(p, grid, smem, stream) : launch_gemv_one<NT, false, false>(p, grid, smem, stream);
 }
 
 inline unsigned blocks_for(int64_t n, int threads) { return static_cast<unsigned>((n + threads - 1) / threads); }
@@ -524,10 +587,43 @@ int hm_gemm(const hm_gemm_desc* desc, int64_t m, const void* a, int64_t lda, con
     return fail(HM_ERR_WORKSPACE, "workspace of %zu bytes given, %lld needed", workspace_bytes, static_cast<long long>(pl.workspace_bytes));
   if (reinterpret_cast<uintptr_t>(workspace) & 255) return fail(HM_ERR_INVALID, "workspace must be 256-byte aligned");
 
+  const bool bf16 = desc->c_dtype == HM_BF16;  // the 16-bit compute type
+  if (pl.mode == 2) {
+    hm::GemvParams gp;
+    memset(&gp, 0, sizeof(gp));
+    const int g = desc->group_size == 0 ? desc->shape_k : desc->group_size;
+    auto ws = static_cast<uint8_t*>(workspace);
+    gp.w = static_cast<const uint8_t*>(w);
+    gp.w_scale = static_cast<const uint8_t*>(w_scale);
+    gp.w_zp = static_cast<const uint8_t*>(w_zp);
+    gp.bias = desc->has_bias ? bias : nullptr;
+    gp.x = a;
+    gp.c = c;
+    gp.status = reinterpret_cast<int*>(ws);
+    gp.counters = reinterpret_cast<int*>(ws + 256);
+    gp.partials = reinterpret_cast<float*>(ws + 256 + ((static_cast<int64_t>(pl.n_tiles) * 4 + 255) / 256) * 256);
+    gp.M = static_cast<int>(m);
+    gp.N = desc->shape_n;
+    gp.K = desc->shape_k;
+    gp.lda = static_cast<int>(lda);
+    gp.ldc = static_cast<int>(ldc);
+    gp.group_size = g;
+    gp.groups = desc->shape_k / g;
+    gp.steps_per_group = g >= hm::kStageK ? g / hm::kStageK : 1;
+    gp.groups_per_step = g >= hm::kStageK ? 1 : hm::kStageK / g;
+    gp.n_tiles = pl.n_tiles;
+    gp.kb_total = pl.kb_per_tile;
+    gp.steps_per_cta = pl.units_per_cta;
+    gp.splits = pl.grid / pl.n_tiles;
+    const int token_rows = m <= 8 ? 8 : 16;
+    const size_t smem = static_cast<size_t>(hm::kGemvStages) * hm::kWStageBytes +
+                        static_cast<size_t>(token_rows) * (pl.units_per_cta * hm::kStageK + hm::kGemvXPad) * 2;
+    auto cs = static_cast<cudaStream_t>(stream);
+    return m <= 8 ? launch_gemv<1>(bf16, desc->has_zp != 0, gp, pl.grid, smem, cs) : launch_gemv<2>(bf16, desc->has_zp != 0, gp, pl.grid, smem, cs);
+  }
   auto encode = tensor_map_encoder();
   if (encode == nullptr) return fail(HM_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   CUtensorMap tmap;
-  const bool bf16 = desc->c_dtype == HM_BF16;  // the 16-bit compute type
   if (a_fp8) {
     // Widen the e4m3 activations (exactly) into the tail of the workspace; the
     // per-token scale is applied to the accumulators in the epilogue.
@@ -943,7 +1039,8 @@ int hm_gemm_static_scratch(const hm_gemm_desc* desc, int64_t m, const void* a, i
   // zero when the kernel starts.  (The partial-sum slots need no clearing, every
   // slot is written before it is read.)
   const int64_t tiles = static_cast<int64_t>(pl.n_tiles) * pl.m_tiles;
-  const size_t zero_bytes = 256 + (pl.mode == 1 ? static_cast<size_t>(((tiles * 16 + 255) / 256) * 256) : 0);
+  size_t zero_bytes = 256 + (pl.mode == 1 ? static_cast<size_t>(((tiles * (pl.cta_pair ? 2 : 1) * 16 + 255) / 256) * 256) : 0);
+  if (pl.mode == 2) zero_bytes = 256 + static_cast<size_t>(((static_cast<int64_t>(pl.n_tiles) * 4 + 255) / 256) * 256);
   HM_CUDA_OK(cudaMemsetAsync(scratch, 0, zero_bytes, static_cast<cudaStream_t>(stream)));
   return hm_gemm(desc, m, a, lda, a_scale, w, w_scale, w_zp, bias, c, ldc, scratch, HM_STATIC_SCRATCH_BYTES, stream);
 }

@@ -273,28 +273,29 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < SW; ++i) {
-      mbar_init(w_full(i), 2);  // code producer + scale/zero-point producer
-      mbar_init(w_empty(i), 4);
+  if (warp == 0) {
+    // One barrier ring per lane (the inits of one thread alone took about 1 000 cycles of every launch).
+    const uint32_t x_full_count = (MOE && !p.a_sorted) ? 32 : 1;  // gathered rows: one arrival per lane of the producer warp
+    const uint32_t pair_count = PAIR ? 8 : 4;                     // pair: both CTAs' warps arrive on the leader's barrier
+    if (lane == 0) for (int i = 0; i < SW; ++i) mbar_init(w_full(i), 2);  // code producer + scale/zero-point producer
+    if (lane == 1) for (int i = 0; i < SW; ++i) mbar_init(w_empty(i), 4);
+    if (lane == 2) for (int i = 0; i < SX; ++i) mbar_init(x_full(i), x_full_count);
+    if (lane == 3) for (int i = 0; i < SX; ++i) mbar_init(x_empty(i), 1);
+    if (lane == 4) for (int i = 0; i < SA; ++i) mbar_init(a_full(i), pair_count);
+    if (lane == 5) for (int i = 0; i < SA; ++i) mbar_init(a_empty(i), 1);
+    if (lane == 6) {
+      for (int i = 0; i < 2; ++i) {
+        mbar_init(acc_full(i), 1);
+        mbar_init(acc_empty(i), pair_count);
+      }
+      mbar_init(drain_bar, 1);
     }
-    for (int i = 0; i < SX; ++i) {
-      mbar_init(x_full(i), (MOE && !p.a_sorted) ? 32 : 1);  // gathered rows: one arrival per lane of the producer warp
-      mbar_init(x_empty(i), 1);
+    if (lane == 7) {
+      for (int e = 0; e < 2; ++e)
+        for (int qq = 0; qq < 4; ++qq) pending[e].last[qq] = 0;
+      abort_flag[0] = 0;  // raised by the first wait that gives up
+      abort_flag[1] = 0;  // separate flag for the drain waits of the abort path
     }
-    for (int i = 0; i < SA; ++i) {
-      mbar_init(a_full(i), PAIR ? 8 : 4);  // pair: both CTAs' dequant warps arrive on the leader's barrier
-      mbar_init(a_empty(i), 1);
-    }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(acc_full(i), 1);
-      mbar_init(acc_empty(i), PAIR ? 8 : 4);
-    }
-    mbar_init(drain_bar, 1);
-    for (int e = 0; e < 2; ++e)
-      for (int qq = 0; qq < 4; ++qq) pending[e].last[qq] = 0;
-    abort_flag[0] = 0;  // raised by the first wait that gives up
-    abort_flag[1] = 0;  // separate flag for the drain waits of the abort path
     mbar_fence_init();
     fence_proxy_async_smem();
   }

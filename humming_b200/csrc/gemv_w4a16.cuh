@@ -1,0 +1,325 @@
+// W4A16 GEMM for 1 to 16 tokens ("decode kernel"): warp-level mma.sync on
+// weights decoded in registers; the packed weights stream through a ring of
+// shared-memory stages filled by bulk copies (cp.async.bulk + mbarrier), the
+// expanded weights are never stored anywhere.
+//
+// Why not tcgen05 here: one tcgen05.mma covers 128 weight rows x 16 K in >= 52
+// cycles whatever the token count (80 measured with the dequant warps running),
+// which alone is 87 % of the HBM time of a 4-bit weight stream, and a launch of
+// the warp-specialised kernel spends 5-6 us in start-up and barrier hand-offs.
+// For a few tokens the work per weight is the decode itself (about two
+// instructions per weight); a warp-level m16n8k16 MMA adds one instruction per
+// 256 weights and takes the decoded pairs straight from registers.
+//
+// Mapping.  A CTA of 4 warps owns one 128-row weight tile and a K range; warp w
+// owns rows 32w .. 32w+31 as two m16 blocks.  One thread keeps kGemvStages
+// stages in flight, each the 8 KB of codes of a 128-K step plus the step's
+// scales and zero points (the same blocks the tensor-memory kernel streams).  In
+// the prepared layout a 16-byte chunk holds 32 consecutive K of one row, word
+// j = K 8j .. 8j+7, and ((word >> 4t) & 0x000F000F) is the pair (K 8j+2t,
+// 8j+2t+1): exactly the pair lane (g, t) = (lane / 4, lane % 4) feeds to the
+// MMA as A-fragment element for row g (or g+8), so every lane decodes only its
+// own pair of every word (w = rn16((q - zp) * s), the same arithmetic as the
+// tensor-memory kernel and hm_dequant_prepared).  Activations are staged once
+// per CTA in shared memory (row pitch padded by 16 bytes: conflict-free
+// B-fragment loads), zero rows above M.  K is split over CTAs; partial sums go
+// to an fp32 workspace and the last CTA of a tile to arrive (atomic counter, no
+// spinning) adds them in split order, so the result does not depend on arrival
+// order.  The waits on the stage barriers are bounded like every wait of the
+// library: on expiry the CTA records a status code and leaves.
+//
+// Same role as the reference's smallest M bucket of humming<>
+// (humming/layer.py:403-451, humming/include/humming/kernel/humming.cuh); the
+// reference has no separate small-M kernel.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "dequant.cuh"
+#include "gemm_w4a16.cuh"  // store_out, load_bias
+#include "ptx.cuh"
+
+namespace hm {
+
+struct GemvParams {
+  const uint8_t* w;        // prepared codes   [n_tile][K/128][4 chunks of 32 K][128 rows][16 B]
+  const uint8_t* w_scale;  // prepared scales  [n_tile][group][128] x 16 bit
+  const uint8_t* w_zp;     // prepared zero points [n_tile][group][64 B] or null
+  const void* bias;        // [N] in the output type, or null
+  const void* x;           // [M, lda] activations, 16 bit
+  void* c;                 // [M, ldc] output, 16 bit
+  float* partials;         // workspace: [splits][M][N] fp32 (splits > 1)
+  int* counters;           // workspace: [n_tiles], zero on entry and on exit
+  int* status;             // workspace: [8], written on abort only
+  int M, N, K;
+  int lda, ldc;
+  int group_size;          // K elements per scale group (64, or a multiple of 128)
+  int groups;              // K / group_size
+  int steps_per_group;     // 128-K steps per scale group (>= 1)
+  int groups_per_step;     // scale groups per 128-K step (1 or 2)
+  int n_tiles;             // N / 128
+  int kb_total;            // K / 128
+  int steps_per_cta;       // 128-K steps per CTA
+  int splits;              // CTAs per tile
+};
+
+constexpr int kGemvThreads = 128;
+constexpr int kGemvXPad = 8;   // elements of padding per activation row in shared memory
+constexpr int kGemvStages = 4;  // packed-weight stages in flight per CTA (8832 bytes each)
+constexpr int HM_ABORT_GEMV_STAGE = 40;
+
+// D (16x8, fp32) += A (16x16, row) * B (16x8, col), 16-bit inputs.
+template <bool BF16>
+HM_DEVICE void mma_m16n8k16(float* d, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  if constexpr (BF16) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  } else {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+}
+
+// The pair (K 2t, 2t+1 of its 8-K word) this lane decodes: one shift + lop3, exact subtract, one rounding multiply.
+template <bool BF16>
+HM_DEVICE uint32_t dequant_pair_u4(uint32_t word, int shift, uint32_t zp_magic2, uint32_t scale2) {
+  const uint32_t t = lop3_and_or(word >> shift, 0x000F000Fu, Magic<BF16>::kBase);
+  return mul2<BF16>(sub2<BF16>(t, zp_magic2), scale2);
+}
+
+// NT: token tiles of 8 (1: up to 8 tokens, 2: up to 16).
+// Dynamic shared memory: [kGemvStages][kWStageBytes] weight stages, then [8 * NT][kc + pad] activations.
+template <int NT, bool BF16, bool HAS_ZP>
+__global__ void __launch_bounds__(kGemvThreads) gemv_w4a16_kernel(const GemvParams p) {
+  extern __shared__ __align__(128) uint8_t gemv_smem[];
+  __shared__ __align__(8) unsigned long long full_bar[kGemvStages];
+  __shared__ __align__(8) unsigned long long empty_bar[kGemvStages];  // one arrival per warp
+  __shared__ int is_last;
+  __shared__ volatile int abort_flag[2];
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int n_tile = blockIdx.x % p.n_tiles;  // neighbouring CTAs share the activation chunk
+  const int split = blockIdx.x / p.n_tiles;
+  const int kb0 = split * p.steps_per_cta;
+  const int kb1 = min(kb0 + p.steps_per_cta, p.kb_total);
+  const int steps = kb1 - kb0;
+  const int kc = steps * 128;
+  const int pitch = kc + kGemvXPad;
+  uint16_t* xs = reinterpret_cast<uint16_t*>(gemv_smem + kGemvStages * kWStageBytes);
+  const uint32_t stage0 = smem_u32(gemv_smem);
+
+  // ---- producer state (thread 0): sources of step kb, as in the tensor-memory kernel's producers
+  const uint8_t* codes_src = p.w + (static_cast<size_t>(n_tile) * p.kb_total + kb0) * (2 * kCodeBytes);
+  const uint32_t scale_bytes = p.groups_per_step * kScaleBytes;
+  const uint32_t zp_bytes = HAS_ZP ? p.groups_per_step * kZpBytes : 0;
+  const uint64_t policy = l2_policy_evict_first();
+  auto group_of_step = [&](int kb) { return p.groups_per_step == 2 ? 2 * kb : kb / p.steps_per_group; };
+  auto issue = [&](int i) {  // step kb0 + i into stage i % kGemvStages
+    const int s = i % kGemvStages;
+    const uint32_t dst = stage0 + s * kWStageBytes;
+    const uint32_t bar = smem_u32(&full_bar[s]);
+    const size_t grp = static_cast<size_t>(n_tile) * p.groups + group_of_step(kb0 + i);
+    mbar_arrive_expect_tx(bar, 2 * kCodeBytes + scale_bytes + zp_bytes);
+    bulk_g2s_hint(dst, codes_src + static_cast<size_t>(i) * (2 * kCodeBytes), 2 * kCodeBytes, bar, policy);
+    bulk_g2s(dst + kWScaleOff, p.w_scale + grp * kScaleBytes, scale_bytes, bar);
+    if constexpr (HAS_ZP) bulk_g2s(dst + kWZpOff, p.w_zp + grp * kZpBytes, zp_bytes, bar);
+  };
+  if (tid == 0) {
+    for (int s = 0; s < kGemvStages; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), kGemvThreads / 32);
+    }
+    abort_flag[0] = 0;
+    abort_flag[1] = 0;
+    mbar_fence_init();
+    fence_proxy_async_smem();
+    // The first stages are requested before anything else: their latency overlaps the activation staging.
+    for (int i = 0; i < kGemvStages && i < steps; ++i) issue(i);
+  }
+
+  // Activations of this K range, 8 values per 16-byte copy; token rows above M are zero.
+  for (int i = tid; i < 8 * NT * (kc / 8); i += kGemvThreads) {
+    const int m = i / (kc / 8);
+    const int j = (i - m * (kc / 8)) * 8;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (m < p.M) v = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.x) + static_cast<size_t>(m) * p.lda + kb0 * 128 + j);
+    *reinterpret_cast<uint4*>(xs + m * pitch + j) = v;
+  }
+  __syncthreads();
+
+  const int wrow = warp * 32 + g;            // this lane's first weight row inside the tile (+ 8, 16, 24)
+  const int row0 = n_tile * 128 + wrow;
+  const int zp_shift = (wrow & 1) * 4;       // rows g + 8k have the parity of g
+  const bool half_group = p.groups_per_step == 2;  // the second 64-K half uses the stage's second group
+
+  // Two accumulator sets (even / odd k16 blocks) halve the length of the dependent MMA chains.
+  float acc2[2][2][NT][4];
+#pragma unroll
+  for (int b = 0; b < 2; ++b)
+#pragma unroll
+    for (int mb = 0; mb < 2; ++mb)
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc2[b][mb][nt][e] = 0.f;
+
+  const int shift = 4 * t;
+  // B fragment of a k16 block: tokens g (+8 for the second tile), K = 2t, 2t+1 and + 8 inside the block.
+  const uint16_t* xb = xs + g * pitch + 2 * t;
+  bool ok = true;
+
+  for (int i = 0; i < steps; ++i) {
+    const int s = i % kGemvStages;
+    if (!mbar_wait_bounded(smem_u32(&full_bar[s]), (i / kGemvStages) & 1, abort_flag)) {
+      if (lane == 0) report_abort(p.status, HM_ABORT_GEMV_STAGE, i, s);
+      ok = false;
+      break;
+    }
+    const uint8_t* st = gemv_smem + s * kWStageBytes;
+    const uint16_t* xk = xb + i * 128;
+    uint32_t scale2[2][4], zpm[2][4];  // [64-K half][row block]
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      if (h == 1 && !half_group) {  // one group per step: both halves share it (warp-uniform)
+#pragma unroll
+        for (int rb = 0; rb < 4; ++rb) {
+          scale2[1][rb] = scale2[0][rb];
+          zpm[1][rb] = zpm[0][rb];
+        }
+        break;
+      }
+#pragma unroll
+      for (int rb = 0; rb < 4; ++rb) {
+        const uint32_t s16 = *reinterpret_cast<const uint16_t*>(st + kWScaleOff + h * kScaleBytes + (wrow + 8 * rb) * 2);
+        scale2[h][rb] = s16 | (s16 << 16);
+        uint32_t zp = 8;
+        if constexpr (HAS_ZP) zp = (st[kWZpOff + h * kZpBytes + ((wrow + 8 * rb) >> 1)] >> zp_shift) & 0xFu;
+        zpm[h][rb] = zp_magic_pair<BF16>(zp);
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {  // 32-K chunk c of row r at byte c * 2048 + r * 16
+      uint4 wq[4];
+#pragma unroll
+      for (int rb = 0; rb < 4; ++rb) wq[rb] = *reinterpret_cast<const uint4*>(st + c * 2048 + (wrow + 8 * rb) * 16);
+#pragma unroll
+      for (int b = 0; b < 2; ++b) {  // two k16 blocks per chunk: words 2b and 2b+1
+        uint32_t bf[NT][2];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          bf[nt][0] = *reinterpret_cast<const uint32_t*>(xk + nt * 8 * pitch + c * 32 + b * 16);
+          bf[nt][1] = *reinterpret_cast<const uint32_t*>(xk + nt * 8 * pitch + c * 32 + b * 16 + 8);
+        }
+#pragma unroll
+        for (int mb = 0; mb < 2; ++mb) {  // rows g, g+8 of m16 block mb = row blocks 2mb, 2mb+1
+          const uint4& lo = wq[2 * mb];
+          const uint4& hi = wq[2 * mb + 1];
+          const uint32_t w_lo0 = b == 0 ? lo.x : lo.z, w_lo1 = b == 0 ? lo.y : lo.w;
+          const uint32_t w_hi0 = b == 0 ? hi.x : hi.z, w_hi1 = b == 0 ? hi.y : hi.w;
+          uint32_t a[4];
+          a[0] = dequant_pair_u4<BF16>(w_lo0, shift, zpm[c >> 1][2 * mb], scale2[c >> 1][2 * mb]);          // row g,   K 2t..
+          a[1] = dequant_pair_u4<BF16>(w_hi0, shift, zpm[c >> 1][2 * mb + 1], scale2[c >> 1][2 * mb + 1]);  // row g+8, K 2t..
+          a[2] = dequant_pair_u4<BF16>(w_lo1, shift, zpm[c >> 1][2 * mb], scale2[c >> 1][2 * mb]);          // row g,   K 8+2t..
+          a[3] = dequant_pair_u4<BF16>(w_hi1, shift, zpm[c >> 1][2 * mb + 1], scale2[c >> 1][2 * mb + 1]);  // row g+8, K 8+2t..
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) mma_m16n8k16<BF16>(acc2[b][mb][nt], a, bf[nt][0], bf[nt][1]);
+        }
+      }
+    }
+    // This warp is done with stage s.  The stage of the step before is refilled one step late, so
+    // that the producer thread rarely has to wait for the other warps.
+    __syncwarp();
+    if (lane == 0) mbar_arrive(smem_u32(&empty_bar[s]));
+    if (tid == 0 && i >= 1 && i - 1 + kGemvStages < steps) {
+      const int sp = (i - 1) % kGemvStages;
+      if (!mbar_wait_bounded(smem_u32(&empty_bar[sp]), ((i - 1) / kGemvStages) & 1, abort_flag)) {
+        report_abort(p.status, HM_ABORT_GEMV_STAGE, i, 100 + sp);
+      } else {
+        issue(i - 1 + kGemvStages);
+      }
+    }
+  }
+  if (!ok) {
+    // Abort path: nothing may land after the CTA has exited.  Stages of steps >= i are in flight at most.
+    __syncthreads();
+    if (tid == 0) {
+      for (int i = 0; i < steps; ++i) mbar_wait_bounded(smem_u32(&full_bar[i % kGemvStages]), (i / kGemvStages) & 1, abort_flag + 1);
+    }
+    __syncthreads();
+    return;
+  }
+
+  float acc[2][NT][4];
+#pragma unroll
+  for (int mb = 0; mb < 2; ++mb)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[mb][nt][e] = acc2[0][mb][nt][e] + acc2[1][mb][nt][e];
+
+  // Accumulator element e of (mb, nt): row 16*mb + g + 8*(e >> 1), token 8*nt + 2t + (e & 1).
+  if (p.splits == 1) {
+#pragma unroll
+    for (int mb = 0; mb < 2; ++mb)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int n = row0 + 16 * mb + 8 * (e >> 1);
+        const float bias = p.bias != nullptr ? load_bias<BF16>(p.bias, n) : 0.f;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const int tok = 8 * nt + 2 * t + (e & 1);
+          if (tok < p.M) store_out<BF16>(p.c, static_cast<size_t>(tok) * p.ldc + n, acc[mb][nt][e] + bias);
+        }
+      }
+    return;
+  }
+#pragma unroll
+  for (int mb = 0; mb < 2; ++mb)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int n = row0 + 16 * mb + 8 * (e >> 1);
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const int tok = 8 * nt + 2 * t + (e & 1);
+        if (tok < p.M) p.partials[(static_cast<size_t>(split) * p.M + tok) * p.N + n] = acc[mb][nt][e];
+      }
+    }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int old = atomicAdd(p.counters + n_tile, 1);
+    is_last = old == p.splits - 1;
+    if (is_last) p.counters[n_tile] = 0;  // leave the workspace clean for the next launch
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  const int n = n_tile * 128 + tid;
+  const float bias = p.bias != nullptr ? load_bias<BF16>(p.bias, n) : 0.f;
+  // Four tokens x eight splits = 32 loads in flight per thread; every sum adds its splits in order.
+  for (int tok0 = 0; tok0 < p.M; tok0 += 4) {
+    float sum[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int s0 = 0; s0 < p.splits; s0 += 8) {
+      float v[4][8];
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          v[q][j] = (tok0 + q < p.M && s0 + j < p.splits)
+                        ? __ldcg(p.partials + (static_cast<size_t>(s0 + j) * p.M + tok0 + q) * p.N + n)
+                        : 0.f;
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sum[q] += v[q][j];
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      if (tok0 + q < p.M) store_out<BF16>(p.c, static_cast<size_t>(tok0 + q) * p.ldc + n, sum[q] + bias);
+  }
+}
+
+}  // namespace hm

@@ -15,7 +15,9 @@ that owns the entry's expert (``all_to_all_single``: rows, local expert ids,
 routing weights), runs the indexed GEMMs over the rows it received (each row is
 its own "token" with top_k = 1), and sends the weighted expert outputs back; the
 source rank un-permutes and sums over top-k.  The exchange is data-dependent,
-so the split sizes travel first (one small all-to-all and a host read).
+so the split sizes travel first (one small all-to-all and a host read); id and
+weight ride in 8 extra bytes per row, so a layer needs three collectives
+(counts, dispatch, combine).
 """
 from typing import Callable, List, Optional, Tuple
 
@@ -61,22 +63,30 @@ class ExpertParallel:
         if self.world == 1:
             rows = hidden.index_select(0, torch.arange(tokens * k, device=hidden.device) // k)
             out = experts_fn(rows, flat_e.int(), flat_w)
-            return out.view(tokens, k, -1)
+            return out.view(tokens, k, out.size(-1))
         dest = flat_e // self.experts_per_rank
         order = torch.argsort(dest, stable=True)
         send_counts = torch.bincount(dest, minlength=self.world)
         in_splits, out_splits = self._exchange_counts(send_counts)
-        rows = hidden.index_select(0, order // k)
-        local_e = (flat_e.index_select(0, order) % self.experts_per_rank).int()
-        w = flat_w.index_select(0, order)
-        recv_rows = self._all_to_all(rows, out_splits, in_splits)
-        recv_e = self._all_to_all(local_e, out_splits, in_splits)
-        recv_w = self._all_to_all(w, out_splits, in_splits)
+        # One exchange carries a row, its local expert id and its routing weight: the row is
+        # extended by 8 bytes holding (int32 id, fp32 weight).
+        width = hidden.size(1)
+        extra = 8 // hidden.element_size()
+        packed = hidden.new_empty((order.numel(), width + extra))
+        packed[:, :width] = hidden.index_select(0, order // k)
+        meta = packed[:, width:].view(torch.int32)
+        meta[:, 0] = (flat_e.index_select(0, order) % self.experts_per_rank).int()
+        meta[:, 1] = flat_w.index_select(0, order).view(torch.int32)
+        recv = self._all_to_all(packed, out_splits, in_splits)
+        recv_meta = recv[:, width:].view(torch.int32)
+        recv_rows = recv[:, :width].contiguous()
+        recv_e = recv_meta[:, 0].contiguous()
+        recv_w = recv_meta[:, 1].contiguous().view(torch.float32)
         out_rows = experts_fn(recv_rows, recv_e, recv_w)
         back = self._all_to_all(out_rows, in_splits, out_splits)
         result = back.new_empty((tokens * k, back.size(-1)))
         result.index_copy_(0, order, back)
-        return result.view(tokens, k, -1)
+        return result.view(tokens, k, back.size(-1))
 
 
 class HummingMoE(torch.nn.Module):

@@ -24,6 +24,8 @@ HM_FLAG_CTA_PAIR = 4
 HM_FLAG_NO_CTA_PAIR = 8
 HM_FLAG_MOE_A_SORTED = 16
 HM_FLAG_MOE_C_SORTED = 32
+HM_FLAG_NO_GEMV = 64
+HM_FLAG_DECODE_KERNEL = 128
 
 
 class GemmDesc(ctypes.Structure):

@@ -207,6 +207,8 @@ def moe_route(logits: torch.Tensor, top_k: int, use_softmax: bool = True, renorm
     tokens, experts = x.shape
     ids = torch.empty((tokens, top_k), dtype=torch.int32, device=x.device)
     wts = torch.empty((tokens, top_k), dtype=torch.float32, device=x.device)
+    if tokens == 0:
+        return ids, wts
     with torch.cuda.device(x.device):
         native.check(native.lib.hm_moe_route(_ptr(x), tokens, experts, top_k, int(use_softmax), int(renormalize), _ptr(ids),
                                              _ptr(wts), _stream(x.device)))
@@ -220,6 +222,8 @@ def silu_mul(x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tenso
     rows, two = x.shape
     if out is None:
         out = torch.empty((rows, two // 2), dtype=x.dtype, device=x.device)
+    if rows == 0:
+        return out
     with torch.cuda.device(x.device):
         native.check(native.lib.hm_silu_mul(_ptr(x), _ptr(out), rows, two // 2, _TORCH_TO_NATIVE[x.dtype], _stream(x.device)))
     return out
@@ -232,6 +236,8 @@ def topk_sum(x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tenso
     tokens, top_k, width = x.shape
     if out is None:
         out = torch.empty((tokens, width), dtype=x.dtype, device=x.device)
+    if tokens == 0:
+        return out
     with torch.cuda.device(x.device):
         native.check(native.lib.hm_topk_sum(_ptr(x), _ptr(out), tokens, top_k, width, _TORCH_TO_NATIVE[x.dtype], _stream(x.device)))
     return out

@@ -95,6 +95,13 @@ typedef struct hm_gemm_desc {
  * counterpart in the reference, whose kernel always gathers and scatters. */
 #define HM_FLAG_MOE_A_SORTED 16
 #define HM_FLAG_MOE_C_SORTED 32
+/* hm_gemm serves one to four tokens of integer 4-bit weights and 16-bit activations with a
+ * decode kernel that decodes the weights in registers and multiplies with warp-level MMAs
+ * (the tcgen05 kernel is bound by its start-up and MMA issue rate there).  NO_GEMV keeps such
+ * calls on the tcgen05 kernel, DECODE_KERNEL extends the decode kernel to up to 16 tokens.
+ * No counterpart in the reference (its M buckets are instantiations of one kernel). */
+#define HM_FLAG_NO_GEMV 64
+#define HM_FLAG_DECODE_KERNEL 128
 
 /* Launch plan chosen for (desc, m); returned by hm_gemm_plan for tests,
  * benchmarks and workspace sizing. */
@@ -103,7 +110,7 @@ typedef struct hm_plan {
   int32_t n_tiles;        /* shape_n / 128 (shape_n / 256 with cta_pair)       */
   int32_t m_tiles;
   int32_t kb_per_tile;    /* shape_k / 128: K steps per tile                   */
-  int32_t mode;           /* 0 = whole tiles round-robin, 1 = contiguous K-split */
+  int32_t mode;           /* 0 = whole tiles round-robin, 1 = contiguous K-split, 2 = decode kernel (m_tile = m, units_per_cta = K steps per CTA) */
   int32_t grid;           /* workers scheduled: CTAs, or CTA pairs with cta_pair */
   int32_t units_per_cta;  /* mode 1: (tile, K step) units per CTA              */
   int32_t cta_pair;       /* 1: clusters of two CTAs, 256 weight rows per tile */

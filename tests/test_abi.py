@@ -68,6 +68,30 @@ def _segments(plan, cta):
     return [tuple(buf[7 * i:7 * i + 7]) for i in range(n)]
 
 
+@pytest.mark.parametrize("n,k", [(128, 128), (6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336), (256, 384)])
+@pytest.mark.parametrize("m", [1, 4, 8, 9, 16, 17])
+def test_gemv_plan_covers_k_and_fits_shared_memory(n, k, m):
+    """Up to 16 tokens go to the decode kernel (mode 2): its K split covers every 128-K step once, a CTA's
+    activations fit the default 48 KB of dynamic shared memory, and the workspace holds every partial sum."""
+    plan = native.Plan()
+    native.check(native.lib.hm_gemm_plan(_desc(shape_n=n, shape_k=k), m, plan))
+    assert (plan.mode == 2) == (m <= 4)                 # by default up to four tokens
+    native.check(native.lib.hm_gemm_plan(_desc(shape_n=n, shape_k=k, flags=native.HM_FLAG_DECODE_KERNEL), m, plan))
+    if m > 16:
+        assert plan.mode != 2
+        return
+    assert plan.mode == 2 and plan.m_tile == m and plan.n_tiles == n // 128 and plan.kb_per_tile == k // 128
+    assert plan.grid % plan.n_tiles == 0
+    splits, steps = plan.grid // plan.n_tiles, plan.units_per_cta
+    assert steps >= 1 and (splits - 1) * steps < plan.kb_per_tile <= splits * steps
+    assert 4 * 8832 + (8 if m <= 8 else 16) * (steps * 128 + 8) * 2 <= 64 * 1024   # weight stages + activations
+    need = 256 + ((plan.n_tiles * 4 + 255) // 256) * 256 + (splits * m * n * 4 if splits > 1 else 0)
+    assert plan.workspace_bytes >= need
+    other = native.Plan()
+    native.check(native.lib.hm_gemm_plan(_desc(shape_n=n, shape_k=k, flags=native.HM_FLAG_NO_SPLIT_K), m, other))
+    assert other.mode == 0          # batch-invariant results were asked for: whole tiles on the tensor cores
+
+
 @pytest.mark.parametrize("n,k,m,flags", [
     (1024, 1024, 16, 0), (28672, 4096, 1, 0), (28672, 4096, 64, 0), (4096, 14336, 16, 0), (4096, 4096, 256, 0),
     (6144, 4096, 1024, 0), (28672, 4096, 8192, 0), (128, 128, 1, 0), (128, 128, 300, 0), (256, 384, 17, 0),
@@ -75,7 +99,9 @@ def _segments(plan, cta):
 ])
 def test_schedule_covers_every_unit_exactly_once(n, k, m, flags):
     plan = native.Plan()
+    flags |= native.HM_FLAG_NO_GEMV   # the tensor-core kernel's scheduler, also for one token
     native.check(native.lib.hm_gemm_plan(_desc(shape_n=n, shape_k=k, flags=flags), m, plan))
+    assert plan.mode in (0, 1)
     tiles = plan.n_tiles * plan.m_tiles
     kb = plan.kb_per_tile
     assert plan.total_units == tiles * kb

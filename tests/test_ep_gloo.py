@@ -27,7 +27,7 @@ def _reference(hidden, ids, wts, weights):
     return out
 
 
-def _worker(rank, world, port, outdir):
+def _worker(rank, world, port, outdir, empty_rank=-1):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -35,7 +35,7 @@ def _worker(rank, world, port, outdir):
         gen = torch.Generator().manual_seed(0)
         weights = torch.randn((E, H, H), generator=gen)           # every rank can build all experts for the check
         gen_r = torch.Generator().manual_seed(10 + rank)          # per-rank tokens
-        tokens = T + rank * 3                                      # ragged: ranks hold different token counts
+        tokens = 0 if rank == empty_rank else T + rank * 3         # ragged: ranks hold different token counts
         hidden = torch.randn((tokens, H), generator=gen_r)
         logits = torch.randn((tokens, E), generator=gen_r)
         if rank == 1:
@@ -69,6 +69,13 @@ def _worker(rank, world, port, outdir):
 
 def test_expert_parallel_dispatch_combine_two_ranks(tmp_path):
     mp.spawn(_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    assert sorted(os.listdir(tmp_path)) == ["ok0", "ok1"]
+
+
+def test_expert_parallel_rank_without_tokens(tmp_path):
+    """A rank that holds no tokens (fewer tokens than ranks) still takes part in the exchange and computes
+    the entries routed to its experts."""
+    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path), 1), nprocs=2, join=True)
     assert sorted(os.listdir(tmp_path)) == ["ok0", "ok1"]
 
 

@@ -348,6 +348,12 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
   if (warp == 0) {
     // ------------------------------------------------ weight producer (packed codes)
     if (lane == 0) {
+      // Weights that are read once (a single token tile per weight tile) are first in line for eviction
+      // from L2; with several token tiles every weight tile is read again and should stay.
+#ifndef HM_W_STREAM_MAX_M_TILES
+#define HM_W_STREAM_MAX_M_TILES 1
+#endif
+      const bool stream_w = MOE || sched.m_tiles <= HM_W_STREAM_MAX_M_TILES;
       const uint64_t pol = l2_policy_evict_first();
       Ring<SW> ring;
       int it = 0;
@@ -367,7 +373,8 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
             mbar_arrive(bar);
           } else {
             mbar_arrive_expect_tx(bar, 2 * kCodeBytes);
-            bulk_g2s_hint(w_smem + ring.idx * kWStageBytes, codes, 2 * kCodeBytes, bar, pol);
+            if (stream_w) bulk_g2s_hint(w_smem + ring.idx * kWStageBytes, codes, 2 * kCodeBytes, bar, pol);
+            else bulk_g2s(w_smem + ring.idx * kWStageBytes, codes, 2 * kCodeBytes, bar);
           }
           trace(0, it, 1);
           codes += 2 * kCodeBytes;

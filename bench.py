@@ -217,18 +217,28 @@ def run_moe(args, rank, world, local_rank):
 
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
-    experts, top_k, hidden, inter = 128, 8, 2048, 768
-    moe = HummingMoE(hidden, inter, experts, top_k).to(dev)
+    w4a8 = args.workload == "moe-w4a8"
+    if w4a8:
+        # BASELINE.json configs[4]: DeepSeek-V3-shaped, 256 experts, top-8, hidden 7168, expert intermediate 2048, int4
+        # symmetric weights, e4m3 activations with per-token scales (quantized inside the layer, before both GEMMs);
+        # bf16 group-128 weight scales (fp32 scales are not a combination the reference accepts either).
+        experts, top_k, hidden, inter = 256, 8, 7168, 2048
+        moe = HummingMoE(hidden, inter, experts, top_k, b_dtype="int4", a_dtype="float8e4m3").to(dev)
+    else:
+        experts, top_k, hidden, inter = 128, 8, 2048, 768
+        moe = HummingMoE(hidden, inter, experts, top_k).to(dev)
+    code_lo, code_hi = (-8, 8) if w4a8 else (0, 16)
     for local, e in enumerate(moe.ep.owned_experts()):
         gen = torch.Generator(device=dev).manual_seed(1000 + e)
-        gu = torch.randint(0, 16, (2 * inter, hidden), generator=gen, dtype=torch.int32, device=dev)
+        gu = torch.randint(code_lo, code_hi, (2 * inter, hidden), generator=gen, dtype=torch.int32, device=dev)
         gus = (torch.randn((2 * inter, hidden // GROUP), generator=gen, device=dev).abs() * 0.02 + 1e-3).bfloat16()
-        dn = torch.randint(0, 16, (hidden, inter), generator=gen, dtype=torch.int32, device=dev)
+        dn = torch.randint(code_lo, code_hi, (hidden, inter), generator=gen, dtype=torch.int32, device=dev)
         dns = (torch.randn((hidden, inter // GROUP), generator=gen, device=dev).abs() * 0.02 + 1e-3).bfloat16()
         moe.load_expert(local, gu, gus, dn, dns)
     moe.finish_load()
     results = []
-    for total_tokens in [int(t) for t in args.tokens.split(",")]:
+    token_list = args.tokens or ("4096,16384,32768" if w4a8 else "1,32,512,4096")
+    for total_tokens in [int(t) for t in token_list.split(",")]:
         tokens = total_tokens // world + (1 if rank < total_tokens % world else 0)
         gen = torch.Generator(device=dev).manual_seed(7 + rank)
         x = torch.randn((tokens, hidden), generator=gen, device=dev).bfloat16()
@@ -264,10 +274,14 @@ def run_moe(args, rank, world, local_rank):
     top = results[-1]
     flops_per_token = 2.0 * top_k * (2 * inter * hidden + hidden * inter)
     line = {
-        "metric": "MoE layer throughput, Qwen3-30B-A3B-shaped (128 experts, top-8, W4A16 bf16)", "value": top["tokens_per_s"],
+        "metric": ("MoE layer throughput, DeepSeek-V3-shaped (256 experts, top-8, W4A8: int4 x e4m3)" if w4a8 else
+                   "MoE layer throughput, Qwen3-30B-A3B-shaped (128 experts, top-8, W4A16 bf16)"), "value": top["tokens_per_s"],
         "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": top["ms_per_step"],
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "qwen3-30b-a3b MoE layer: route, align, up GEMM, silu*mul, down GEMM, top-k sum",
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16 tensor path after exact widening of the e4m3 activations" if w4a8 else "bf16", "data": "synthetic",
+        "config": {"workload": ("deepseek-v3" if w4a8 else "qwen3-30b-a3b") + " MoE layer: route, align, gather, " +
+                               ("quantize, " if w4a8 else "") + "up GEMM, silu*mul, " + ("quantize, " if w4a8 else "") +
+                               "down GEMM, top-k sum",
                    "experts": experts, "top_k": top_k, "hidden": hidden, "intermediate": inter, "tokens_total": top["tokens"],
                    "parallelism": f"ep{world}" if world > 1 else "single GPU",
                    "timing": "one GPU: CUDA graph of a forward replayed K times; expert parallel: eager (the exchange sizes are read on the host); "
@@ -555,8 +569,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="dense", choices=["dense", "moe", "mxfp4"])
-    ap.add_argument("--tokens", default="1,32,512,4096", help="moe workload: total token counts to time, the last one is the headline")
+    ap.add_argument("--workload", default="dense", choices=["dense", "moe", "moe-w4a8", "mxfp4"])
+    ap.add_argument("--tokens", default=None, help="moe workload: total token counts to time, the last one is the headline")
     ap.add_argument("--native-flags", type=int, default=0, help="HM_FLAG_* bits OR-ed into every dense GEMM descriptor (kernel A/B comparisons)")
     ap.add_argument("--point", default=None, help="PROJ:M, e.g. gate_up:16 -- launch only this sweep point a few times")
     args = ap.parse_args()
@@ -578,7 +592,7 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     try:
-        if args.workload == "moe":
+        if args.workload in ("moe", "moe-w4a8"):
             run_moe(args, rank, world, local_rank)
         else:
             run_ours(args, rank, world, local_rank)

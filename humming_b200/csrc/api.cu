@@ -176,10 +176,10 @@ int make_plan(const hm_gemm_desc* d, int64_t m, hm_plan* plan) {
     memset(plan, 0, sizeof(*plan));
     const int kb = d->shape_k / hm::kStageK;
     const int n_tiles = d->shape_n / hm::kTileN;
-    // K steps per CTA: as many waves of four CTAs per SM as needed, each lasting its steps plus
+    // K steps per CTA: as many waves of resident CTAs as needed, each lasting its steps plus
     // about three steps' worth of start-up and partial-sum traffic; the cheapest count wins.
     const int max_steps = m <= 8 ? 8 : 4;  // a CTA's activations in shared memory: about 16 KB
-    const int slots = 4 * sms;
+    const int slots = hm::kGemvCtasPerSm * sms;
     int steps = 1;
     int64_t best_cost = -1;
     for (int cand = 1; cand <= max_steps && cand <= kb; ++cand) {

@@ -773,8 +773,45 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
       constexpr int CH = MT >= 32 ? 32 : 16;  // token columns per chunk
       // This warp's [tokens][32 rows] 16-bit tile: one chunk of CH tokens, or the whole tile when staged.
       uint8_t* stage_base = smem_gen + Cfg::SMEM_STAGE + q * Cfg::EPI_WARP_BYTES;
+      bool drained = false;
+      if constexpr (Cfg::STAGED_EPI) {
+        if (!seg.partial) {
+          // Pipelined drain into the staging tile: the tensor-memory load of the next 16 token
+          // columns is in flight while 16 are converted (the accumulator is handed back right after).
+          const bool scaled = p.act_scale != nullptr;  // warp-uniform
+          auto convert16 = [&](const uint32_t* r, int c0) {
+            float col_s = 1.f;
+            if (scaled && lane < 16 && c0 + lane < m_valid) col_s = p.act_scale[m0 + c0 + lane];
+            uint8_t* st = stage_base + c0 * 64;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              float o = __uint_as_float(r[j]);
+              o = scaled ? fmaf(o, __shfl_sync(0xffffffffu, col_s, j), bias) : o + bias;
+              if constexpr (BF16) {
+                reinterpret_cast<__nv_bfloat16*>(st)[j * 32 + lane] = __float2bfloat16_rn(o);
+              } else {
+                reinterpret_cast<__half*>(st)[j * 32 + lane] = __float2half_rn(o);
+              }
+            }
+          };
+          uint32_t ra[16], rb[16];
+          tmem_ld_x16(t_acc, ra);
 #pragma unroll 1
-      for (int c0 = 0; c0 < MT; c0 += CH) {
+          for (int c0 = 0; c0 < MT && c0 < m_valid; c0 += 32) {
+            tc_wait_ld();
+            tmem_ld_x16(t_acc + c0 + 16, rb);
+            convert16(ra, c0);
+            tc_wait_ld();
+            if (c0 + 32 < MT) tmem_ld_x16(t_acc + c0 + 32, ra);
+            convert16(rb, c0 + 16);
+          }
+          tc_wait_ld();  // the load issued ahead of the last chunk
+          __syncwarp();
+          drained = true;
+        }
+      }
+#pragma unroll 1
+      for (int c0 = 0; c0 < MT && !drained; c0 += CH) {
         if (c0 >= m_valid) break;  // warp-uniform
         float v[CH];
         {

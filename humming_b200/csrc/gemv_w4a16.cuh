@@ -65,7 +65,12 @@ struct GemvParams {
 
 constexpr int kGemvThreads = 128;
 constexpr int kGemvXPad = 8;   // elements of padding per activation row in shared memory
-constexpr int kGemvStages = 4;  // packed-weight stages in flight per CTA (8832 bytes each)
+#ifndef HM_GEMV_STAGES
+#define HM_GEMV_STAGES 4
+#endif
+constexpr int kGemvStages = HM_GEMV_STAGES;  // packed-weight stages in flight per CTA (8832 bytes each)
+// CTAs that fit an SM with that many stages plus about 16 KB of activations (shared memory is the limit).
+constexpr int kGemvCtasPerSm = kGemvStages == 2 ? 7 : kGemvStages == 3 ? 5 : 4;
 constexpr int HM_ABORT_GEMV_STAGE = 40;
 
 // D (16x8, fp32) += A (16x16, row) * B (16x8, col), 16-bit inputs.

@@ -169,8 +169,8 @@ def run_reference(args, rank, world):
 
 
 # DRAM bytes per launch from the ncu captures summarised under profiles/ (read + write).
-NCU_DRAM_BYTES_GATE_UP_4096 = 1.044e9   # profiles/gemm_w4a16_gate_up_m4096_prefill.md (algorithmic: 0.329e9)
-NCU_DRAM_BYTES_GATE_UP_16 = 61.5e6      # profiles/gemm_w4a16_gate_up_m16_decode.md
+NCU_DRAM_BYTES_GATE_UP_4096 = 0.552e9   # profiles/gemm_w4a16_gate_up_m4096_prefill.md (algorithmic: 0.329e9)
+NCU_DRAM_BYTES_GATE_UP_16 = 61.7e6      # profiles/gemm_w4a16_gate_up_m16_decode.md
 
 
 def run_point(args):

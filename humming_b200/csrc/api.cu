@@ -102,6 +102,12 @@ int validate_desc(const hm_gemm_desc* d) {
 // kernel: by default up to 4 (measured faster there on B200, 10-35 %; about equal at 8, slower at 16),
 // up to 16 when HM_FLAG_DECODE_KERNEL asks for it.
 constexpr int kGemvPlanMaxM = 4;
+constexpr int kGemvFmaMaxM = 1;   // of those, a single token uses plain fp32 multiply-adds (measured slower than the MMA form at two)
+#ifndef HM_GEMV_OVERHEAD_STEPS
+#define HM_GEMV_OVERHEAD_STEPS 10
+#endif
+// Start-up, activation staging and partial-sum traffic of a decode CTA, in units of one 128-K step.
+constexpr int kGemvCtaOverheadSteps = HM_GEMV_OVERHEAD_STEPS;
 constexpr int kGemvKernelMaxM = 16;
 
 // One way to run (desc, m): token tile, one CTA or a CTA pair per weight tile,
@@ -177,15 +183,16 @@ int make_plan(const hm_gemm_desc* d, int64_t m, hm_plan* plan) {
     const int kb = d->shape_k / hm::kStageK;
     const int n_tiles = d->shape_n / hm::kTileN;
     // K steps per CTA: as many waves of resident CTAs as needed, each lasting its steps plus
-    // about three steps' worth of start-up and partial-sum traffic; the cheapest count wins.
-    const int max_steps = m <= 8 ? 8 : 4;  // a CTA's activations in shared memory: about 16 KB
+    // a fixed start-up / partial-sum cost; the cheapest count wins.
+    // A CTA's activations in shared memory: about 16 KB (fp32 for one or two tokens, 16 bit in 8 / 16 token rows).
+    const int max_steps = m <= kGemvFmaMaxM && !(d->flags & HM_FLAG_DECODE_KERNEL) ? 32 / static_cast<int>(m) : (m <= 8 ? 8 : 4);
     const int slots = hm::kGemvCtasPerSm * sms;
     int steps = 1;
     int64_t best_cost = -1;
     for (int cand = 1; cand <= max_steps && cand <= kb; ++cand) {
       const int64_t ctas = static_cast<int64_t>(n_tiles) * ((kb + cand - 1) / cand);
       const int64_t waves = (ctas + slots - 1) / slots;
-      const int64_t cost = waves * (cand + 3);
+      const int64_t cost = waves * (cand + kGemvCtaOverheadSteps);
       if (best_cost < 0 || cost <= best_cost) best_cost = cost, steps = cand;
     }
     const int splits = (kb + steps - 1) / steps;
@@ -387,6 +394,28 @@ int launch_gemv_one(const hm::GemvParams& p, int grid, size_t smem, cudaStream_t
   kern<<<grid, hm::kGemvThreads, smem, stream>>>(p);
   HM_CUDA_OK(cudaGetLastError());
   return HM_OK;
+}
+
+template <int MT, bool BF16, bool HAS_ZP>
+int launch_gemv_fma_one(const hm::GemvParams& p, int grid, size_t smem, cudaStream_t stream) {
+  auto kern = hm::gemv_fma_w4a16_kernel<MT, BF16, HAS_ZP>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  HM_CUDA_OK(cudaGetDevice(&dev));
+  if (!configured[dev & 63]) {
+    HM_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemvMaxSmem)));
+    configured[dev & 63] = true;
+  }
+  if (smem > kGemvMaxSmem) return fail(HM_ERR_INVALID, "decode kernel: %zu bytes of shared memory asked for", smem);
+  kern<<<grid, hm::kGemvThreads, smem, stream>>>(p);
+  HM_CUDA_OK(cudaGetLastError());
+  return HM_OK;
+}
+
+template <int MT>
+int launch_gemv_fma(bool bf16, bool zp, const hm::GemvParams& p, int grid, size_t smem, cudaStream_t stream) {
+  if (bf16) return zp ? launch_gemv_fma_one<MT, true, true>(p, grid, smem, stream) : launch_gemv_fma_one<MT, true, false>(p, grid, smem, stream);
+  return zp ? launch_gemv_fma_one<MT, false, true>(p, grid, smem, stream) : launch_gemv_fma_one<MT, false, false>(p, grid, smem, stream);
 }
 
 template <int NT>
@@ -615,10 +644,18 @@ int hm_gemm(const hm_gemm_desc* desc, int64_t m, const void* a, int64_t lda, con
     gp.kb_total = pl.kb_per_tile;
     gp.steps_per_cta = pl.units_per_cta;
     gp.splits = pl.grid / pl.n_tiles;
+    auto cs = static_cast<cudaStream_t>(stream);
+    if (m <= kGemvFmaMaxM && !(desc->flags & HM_FLAG_DECODE_KERNEL)) {
+      // a single token: fp32 multiply-adds (the flag asks for the MMA form, which the tests compare with)
+      const size_t smem_fma = static_cast<size_t>(hm::kGemvStages) * hm::kWStageBytes +
+                              static_cast<size_t>(m) * (pl.units_per_cta * hm::kStageK + 2 * pl.units_per_cta) * 4;
+      return m == 1 ? launch_gemv_fma<1>(bf16, desc->has_zp != 0, gp, pl.grid, smem_fma, cs)
+                    : launch_gemv_fma<2>(bf16, desc->has_zp != 0, gp, pl.grid, smem_fma, cs);
+    }
     const int token_rows = m <= 8 ? 8 : 16;
     const size_t smem = static_cast<size_t>(hm::kGemvStages) * hm::kWStageBytes +
-                        static_cast<size_t>(token_rows) * (pl.units_per_cta * hm::kStageK + hm::kGemvXPad) * 2;
-    auto cs = static_cast<cudaStream_t>(stream);
+                        static_cast<size_t>(token_rows) * (pl.units_per_cta * hm::kStageK + hm::kGemvXPad) * 2 +
+                        static_cast<size_t>(token_rows) * 2 * pl.units_per_cta * 4;  // activation sums per 64-K half step
     return m <= 8 ? launch_gemv<1>(bf16, desc->has_zp != 0, gp, pl.grid, smem, cs) : launch_gemv<2>(bf16, desc->has_zp != 0, gp, pl.grid, smem, cs);
   }
   auto encode = tensor_map_encoder();

@@ -84,7 +84,8 @@ def test_gemv_plan_covers_k_and_fits_shared_memory(n, k, m):
     assert plan.grid % plan.n_tiles == 0
     splits, steps = plan.grid // plan.n_tiles, plan.units_per_cta
     assert steps >= 1 and (splits - 1) * steps < plan.kb_per_tile <= splits * steps
-    assert 4 * 8832 + (8 if m <= 8 else 16) * (steps * 128 + 8) * 2 <= 64 * 1024   # at most four weight stages + activations
+    x_bytes = m * (steps * 128 + 2 * steps) * 4 if m <= 1 else (8 if m <= 8 else 16) * (steps * 128 + 8 + 4 * steps) * 2
+    assert 4 * 8832 + x_bytes <= 64 * 1024   # at most four weight stages + activations (+ their sums)
     need = 256 + ((plan.n_tiles * 4 + 255) // 256) * 256 + (splits * m * n * 4 if splits > 1 else 0)
     assert plan.workspace_bytes >= need
     other = native.Plan()

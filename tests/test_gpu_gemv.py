@@ -28,12 +28,23 @@ def test_gemv_matches_oracle(cuda_device, dtype, zp, m):
     assert_close_16(out, ref, f"gemv m={m}")
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("zp", [False, True])
+@pytest.mark.parametrize("m", [1])
+def test_gemv_fma_form_matches_oracle(cuda_device, dtype, zp, m):
+    """A single token runs the fp32 multiply-add form by default."""
+    case = synthetic.dense_w4a16_case(512, 2048, dtype, zp, seed=19)
+    out, ref, layer = run_case(case, m, cuda_device)
+    assert plan_of(layer, m).mode == 2
+    assert_close_16(out, ref, f"gemv fma m={m}")
+
+
 @pytest.mark.parametrize("n,k,g", [(128, 128, 64), (128, 128, 128), (256, 4096, 128), (2048, 256, 64), (384, 1024, 0), (1536, 2048, 256),
                                    (128, 14336, 128)])
 def test_gemv_shapes_and_groups(cuda_device, n, k, g):
     case = synthetic.dense_w4a16_case(n, k, torch.bfloat16, True, group_size=g or k, seed=5)
-    for m in (3, 11):
-        out, ref, _ = run_case(case, m, cuda_device, flags=native.HM_FLAG_DECODE_KERNEL)
+    for m, flags in ((3, native.HM_FLAG_DECODE_KERNEL), (11, native.HM_FLAG_DECODE_KERNEL), (1, 0), (2, 0)):
+        out, ref, _ = run_case(case, m, cuda_device, flags=flags)
         assert_close_16(out, ref, f"gemv n={n} k={k} g={g} m={m}")
 
 
@@ -64,7 +75,9 @@ def test_gemv_llama_shapes_against_gpu_fp32(cuda_device, name):
     layer, _ = build_layer(case)
     layer.humming_kernel_options[""]["native_flags"] = native.HM_FLAG_DECODE_KERNEL
     w = runtime.dequant_prepared(HummingMethod._desc(layer.meta), layer.weight, layer.weight_scale, layer.zero_point)
-    for m in (1, 4, 16):
+    for m in (1, 4, 16, -1, -2):   # negative: default plan (fp32 multiply-add form for one or two tokens)
+        layer.humming_kernel_options[""]["native_flags"] = native.HM_FLAG_DECODE_KERNEL if m > 0 else 0
+        m = abs(m)
         x = synthetic.activations(m, k, torch.bfloat16).to(cuda_device)
         out = layer(inputs=x)
         assert_close_16(out, (x.float() @ w.T).to(torch.bfloat16), f"gemv {name} m={m}")

@@ -45,7 +45,8 @@ class ExpertParallel:
     def _exchange_counts(self, send_counts: torch.Tensor) -> Tuple[List[int], List[int]]:
         recv_counts = torch.empty_like(send_counts)
         dist.all_to_all_single(recv_counts, send_counts, group=self.group)
-        return send_counts.tolist(), recv_counts.tolist()
+        both = torch.stack((send_counts, recv_counts)).tolist()   # one host read for both
+        return both[0], both[1]
 
     def _all_to_all(self, x: torch.Tensor, out_splits: List[int], in_splits: List[int]) -> torch.Tensor:
         out = x.new_empty((sum(out_splits),) + tuple(x.shape[1:]))

@@ -70,6 +70,28 @@ def test_static_scratch_matches_workspace_path_twice(cuda_device):
     torch.testing.assert_close(got_s.float(), want_s.float(), atol=ATOL_16, rtol=RTOL_16)
 
 
+def test_static_scratch_serves_the_decode_kernels(cuda_device):
+    """One and three tokens are planned for the decode kernels (mode 2), whose counters and partial sums
+    live in the same array; twice in a row, after a tensor-core call has left its own data there."""
+    case = synthetic.dense_w4a16_case(1024, 4096, torch.bfloat16, True, seed=33)
+    layer, _ = build_layer(case)
+    desc = HummingMethod._desc(layer.meta)
+    x16 = synthetic.activations(16, 4096, torch.bfloat16, seed=44).to(cuda_device)
+    native.check(_call_static(layer, desc, x16, torch.empty((16, 1024), dtype=torch.bfloat16, device=cuda_device)))
+    for m in (1, 3):
+        plan = native.Plan()
+        native.check(native.lib.hm_gemm_plan(ctypes.byref(desc), m, ctypes.byref(plan)))
+        assert plan.mode == 2 and plan.workspace_bytes <= native.HM_STATIC_SCRATCH_BYTES
+        x = synthetic.activations(m, 4096, torch.bfloat16, seed=45 + m).to(cuda_device)
+        want = layer(inputs=x).clone()
+        for _ in range(2):
+            got = torch.empty_like(want)
+            native.check(_call_static(layer, desc, x, got))
+            torch.cuda.synchronize()
+            assert torch.equal(got, want)
+    layer.check_status()
+
+
 def test_static_scratch_refuses_shapes_beyond_its_size(cuda_device):
     # a long K with few tiles: planned as a K split whose partial tiles exceed the static array
     case = synthetic.dense_w4a16_case(2048, 8192, torch.bfloat16, True, seed=31)

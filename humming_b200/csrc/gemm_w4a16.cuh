@@ -314,6 +314,10 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
   if constexpr (PAIR) cluster_sync_all();  // the peer's barriers are initialised before anyone signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  // Barrier set-up and the tensor-memory allocation above may overlap the previous kernel of the stream; from
+  // here on global memory is touched (activations, workspace, outputs), so that kernel must have completed.
+  grid_dep_launch();
+  grid_dep_wait();
 
   SchedParams sched = p.sched;
   if constexpr (MOE) {

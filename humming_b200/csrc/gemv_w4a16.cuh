@@ -187,6 +187,10 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_fma_w4a16_kernel(const Gemv
     fence_proxy_async_smem();
     for (int i = 0; i < kGemvStages && i < steps; ++i) issue(i);
   }
+  // The weights are constant, so the requests above may overlap the previous kernel of the stream;
+  // activations, workspace and outputs are touched only after it has completed.
+  grid_dep_launch();
+  grid_dep_wait();
 
   // Activations of this K range as fp32 (token rows above M are zero), then their sums per half step.
   for (int i = tid; i < MT * (kc / 8); i += kGemvThreads) {
@@ -379,6 +383,10 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_w4a16_kernel(const GemvPara
     // The first stages are requested before anything else: their latency overlaps the activation staging.
     for (int i = 0; i < kGemvStages && i < steps; ++i) issue(i);
   }
+  // The weights are constant, so the requests above may overlap the previous kernel of the stream;
+  // activations, workspace and outputs are touched only after it has completed.
+  grid_dep_launch();
+  grid_dep_wait();
 
   // Activations of this K range, 8 values per 16-byte copy; token rows above M are zero.
   for (int i = tid; i < 8 * NT * (kc / 8); i += kGemvThreads) {

@@ -148,6 +148,15 @@ HM_DEVICE bool mbar_wait_bounded_cluster(uint32_t bar, uint32_t parity, volatile
 // inside a 2-CTA cluster the rank is bit 24 of a shared::cluster address.
 HM_DEVICE uint32_t leader_smem_addr(uint32_t addr) { return addr & 0xFEFFFFFFu; }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-stream-serialization attribute may start while the kernel before it
+// in the stream is still running: everything it does before grid_dep_wait() overlaps that kernel's tail.
+// grid_dep_wait() returns once every prerequisite grid has completed and its memory is visible (a no-op for
+// a plain launch); grid_dep_launch() lets the next kernel's launch begin once all CTAs of this grid have
+// called it (they have all started by then, so the next grid cannot take their place).
+HM_DEVICE void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+HM_DEVICE void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---------------------------------------------------------------- fences
 HM_DEVICE void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

@@ -316,8 +316,10 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
   const uint32_t tmem_base = *tmem_holder;
   // Barrier set-up and the tensor-memory allocation above may overlap the previous kernel of the stream; from
   // here on global memory is touched (activations, workspace, outputs), so that kernel must have completed.
+  // The two weight producers (warps 0 and 3) of the dense GEMM only read the prepared weights, which no
+  // kernel writes, and follow a schedule known at launch: they start filling the weight ring right away.
   grid_dep_launch();
-  grid_dep_wait();
+  if (MOE || !(warp == 0 || warp == 3)) grid_dep_wait();
 
   SchedParams sched = p.sched;
   if constexpr (MOE) {

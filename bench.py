@@ -590,7 +590,9 @@ def main():
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        import datetime
+        # A collective that does not complete within five minutes ends the run with an error instead of hanging.
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=datetime.timedelta(minutes=5))
     try:
         if args.workload in ("moe", "moe-w4a8"):
             run_moe(args, rank, world, local_rank)

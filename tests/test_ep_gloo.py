@@ -79,6 +79,41 @@ def test_expert_parallel_rank_without_tokens(tmp_path):
     assert sorted(os.listdir(tmp_path)) == ["ok0", "ok1"]
 
 
+def test_expert_parallel_four_ranks_mostly_without_tokens(tmp_path):
+    """Four ranks, only rank 0 holds tokens (a single-token batch spread over many GPUs)."""
+    mp.spawn(_worker4, args=(4, _free_port(), str(tmp_path)), nprocs=4, join=True)
+    assert sorted(os.listdir(tmp_path)) == ["ok0", "ok1", "ok2", "ok3"]
+
+
+def _worker4(rank, world, port, outdir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        gen = torch.Generator().manual_seed(0)
+        weights = torch.randn((E, H, H), generator=gen)
+        tokens = 1 if rank == 0 else 0
+        hidden = torch.randn((tokens, H), generator=gen).bfloat16()       # 16-bit rows: id and weight ride in 4 extra elements
+        logits = torch.randn((tokens, E), generator=gen)
+        wts, ids = torch.softmax(logits, -1).topk(K, 1)
+        ep = ExpertParallel(E)
+
+        def experts_fn(rows, local_e, w):
+            out = torch.empty_like(rows)
+            for i in range(rows.size(0)):
+                out[i] = (w[i] * (rows[i].float() @ weights[rank * ep.experts_per_rank + int(local_e[i])])).to(rows.dtype)
+            return out
+
+        got = ep.forward(hidden, ids.int(), wts, experts_fn)
+        assert got.shape == (tokens, K, H)
+        if tokens:
+            want = torch.stack([(wts[0, j] * (hidden[0].float() @ weights[ids[0, j]])).bfloat16() for j in range(K)])
+            torch.testing.assert_close(got[0].float(), want.float(), rtol=2e-2, atol=2e-2)
+        open(os.path.join(outdir, f"ok{rank}"), "w").close()
+    finally:
+        dist.destroy_process_group()
+
+
 def test_single_rank_path_needs_no_process_group():
     gen = torch.Generator().manual_seed(0)
     weights = torch.randn((E, H, H), generator=gen)

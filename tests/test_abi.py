@@ -138,3 +138,29 @@ def test_schedule_covers_every_unit_exactly_once(n, k, m, flags):
     if plan.mode == 1:
         need = 256 + ((tiles * 16 + 255) // 256) * 256 + plan.grid * 2 * plan.m_tile * 128 * 4
         assert plan.workspace_bytes >= need
+
+
+@pytest.mark.parametrize("n,k,m,expect", [
+    # (token tile, mode, CTA pair) the launch plan picks on a 148-SM GPU for the Llama-3-8B projections
+    (6144, 4096, 1, (1, 2, 0)), (28672, 4096, 4, (4, 2, 0)),              # decode kernels
+    (28672, 4096, 16, (16, 1, 0)), (4096, 14336, 16, (16, 1, 0)),        # 16-token tile, K split
+    (28672, 4096, 64, (64, 0, 0)), (4096, 4096, 64, (32, 1, 0)),
+    (6144, 4096, 256, (128, 0, 0)), (4096, 14336, 256, (128, 1, 0)), (28672, 4096, 256, (256, 0, 1)),
+    (4096, 4096, 1024, (256, 0, 1)), (28672, 4096, 8192, (256, 0, 1)), (4096, 14336, 4096, (256, 0, 1)),
+])
+def test_plan_choices_for_llama_shapes(n, k, m, expect):
+    plan = native.Plan()
+    native.check(native.lib.hm_gemm_plan(_desc(shape_n=n, shape_k=k, num_sms=148), m, plan))
+    assert (plan.m_tile, plan.mode, plan.cta_pair) == expect
+
+
+def test_plan_pair_needs_256_row_multiples_and_flags_override():
+    plan = native.Plan()
+    native.check(native.lib.hm_gemm_plan(_desc(shape_n=4096 + 128, shape_k=4096, num_sms=148), 4096, plan))
+    assert plan.cta_pair == 0                                     # 33 tiles of 128 rows: no pairs
+    native.check(native.lib.hm_gemm_plan(_desc(shape_n=4096, shape_k=4096, num_sms=148, flags=native.HM_FLAG_NO_CTA_PAIR), 4096, plan))
+    assert plan.cta_pair == 0 and plan.m_tile == 256
+    native.check(native.lib.hm_gemm_plan(_desc(shape_n=4096, shape_k=4096, num_sms=148, flags=native.HM_FLAG_CTA_PAIR), 100, plan))
+    assert plan.cta_pair == 1 and plan.m_tile in (32, 64, 128)
+    native.check(native.lib.hm_gemm_plan(_desc(shape_n=4096, shape_k=4096, num_sms=148, m_tile=192), 4096, plan))
+    assert plan.cta_pair == 0 and plan.m_tile == 192              # the 192-token tile has no pair kernel

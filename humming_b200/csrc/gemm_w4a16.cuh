@@ -315,11 +315,11 @@ gemm_w4a16_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
   // Barrier set-up and the tensor-memory allocation above may overlap the previous kernel of the stream; from
-  // here on global memory is touched (activations, workspace, outputs), so that kernel must have completed.
-  // The two weight producers (warps 0 and 3) of the dense GEMM only read the prepared weights, which no
-  // kernel writes, and follow a schedule known at launch: they start filling the weight ring right away.
+  // here on global memory is touched (weights, activations, workspace, outputs), so that kernel must have
+  // completed.  (Letting the weight producers start earlier saved another microsecond per small launch, but
+  // the kernel before this one may be the very repack kernel that writes the prepared weights.)
   grid_dep_launch();
-  if (MOE || !(warp == 0 || warp == 3)) grid_dep_wait();
+  grid_dep_wait();
 
   SchedParams sched = p.sched;
   if constexpr (MOE) {

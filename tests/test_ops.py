@@ -1,0 +1,109 @@
+"""CPU checks of the operator-level surface (``torch.ops.humming.*``): the schemas are the reference's
+(``humming/csrc/launcher/launcher.cpp:220-224``, ``humming/kernel/quant_input.py:144-150``), shape inference
+follows ``humming/csrc/launcher/tensor.h:9-20``, and there is no CPU implementation to fall back to."""
+import pytest
+import torch
+
+from humming_b200 import native, ops, runtime
+from humming_b200.layer import HummingLayer, HummingMethod
+
+REFERENCE_LAUNCH_SCHEMA = (
+    "humming::launch_humming(int[] configs, Tensor a, Tensor b, Tensor(c!)? c, Tensor? as_, Tensor? bs, Tensor? bzp, "
+    "Tensor? bias, Tensor? gs, Tensor? topk_weights, Tensor? sorted_token_ids, Tensor? expert_ids, "
+    "Tensor? num_tokens_post_padded, Tensor(locks!)? locks, int num_ctas_per_sm=1, int? num_sms=None, "
+    "bool should_check_tensor=True) -> Tensor")
+REFERENCE_QUANT_SCHEMA = ("humming::humming_quant_input(Tensor inputs, str dtype, Tensor? scales=None, "
+                          "int? group_size=None) -> (Tensor, Tensor)")
+
+
+def _launch(configs, a, c=None, **kw):
+    b = torch.empty((1,), dtype=torch.int32, device=a.device)
+    args = dict(as_=None, bs=None, bzp=None, bias=None, gs=None, topk_weights=None, sorted_token_ids=None,
+                expert_ids=None, num_tokens_post_padded=None, locks=None)
+    args.update(kw)
+    return torch.ops.humming.launch_humming(configs, a, b, c, *args.values())
+
+
+def test_schemas_are_the_reference_ones():
+    assert str(torch.ops.humming.launch_humming.default._schema) == REFERENCE_LAUNCH_SCHEMA
+    assert str(torch.ops.humming.humming_quant_input.default._schema) == REFERENCE_QUANT_SCHEMA
+
+
+def test_configs_round_trip_and_tile_table():
+    desc = runtime.make_desc(1024, 512, "bfloat16", "uint4", "bfloat16", "bfloat16", group_size=128, has_zp=True,
+                             flags=native.HM_FLAG_NO_SPLIT_K)
+    configs = ops.desc_to_configs(desc, [1, 16, 16, 17, 1 << 31, 256])
+    assert len(configs) == len(native.GemmDesc._fields_) + 6
+    for m, tile in ((1, 16), (16, 16), (17, 256), (100000, 256), (0, 0)):
+        back = ops.configs_to_desc(configs, m)
+        assert back.m_tile == tile
+        for name, _ in native.GemmDesc._fields_:
+            if name != "m_tile":
+                assert getattr(back, name) == getattr(desc, name), name
+    with pytest.raises(ValueError):
+        ops.configs_to_desc(configs[:5], 1)
+    with pytest.raises(ValueError):
+        ops.configs_to_desc(configs + [1], 1)
+    with pytest.raises(ValueError):
+        ops.desc_to_configs(desc, [1, 2])
+
+
+@pytest.mark.parametrize("device", ["meta", "fake"])
+def test_output_shapes_dense_and_moe(device):
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    dense = ops.desc_to_configs(runtime.make_desc(1024, 512, "float16", "uint4", "float16", "float16", group_size=128))
+    up = ops.desc_to_configs(runtime.make_desc(1536, 2048, "bfloat16", "uint4", "bfloat16", "bfloat16", group_size=128,
+                                               num_experts=128, top_k=8))
+    down = ops.desc_to_configs(runtime.make_desc(2048, 768, "bfloat16", "uint4", "bfloat16", "bfloat16", group_size=128,
+                                                 num_experts=128, top_k=8, is_moe_down=True))
+    mode = FakeTensorMode() if device == "fake" else None
+    dev = "cuda" if device == "fake" else "meta"     # fake CUDA tensors need no GPU
+    if mode:
+        mode.__enter__()
+    try:
+        out = _launch(dense, torch.empty((3, 5, 512), dtype=torch.float16, device=dev))
+        assert tuple(out.shape) == (3, 5, 1024) and out.dtype == torch.float16 and out.device.type == dev
+        out = _launch(up, torch.empty((7, 2048), dtype=torch.bfloat16, device=dev))
+        assert tuple(out.shape) == (7, 8, 1536) and out.dtype == torch.bfloat16
+        out = _launch(down, torch.empty((7, 8, 768), dtype=torch.bfloat16, device=dev))
+        assert tuple(out.shape) == (7, 8, 2048)
+        given = torch.empty((15, 1024), dtype=torch.float16, device=dev)
+        assert _launch(dense, torch.empty((15, 512), dtype=torch.float16, device=dev), given) is given
+        q, s = torch.ops.humming.humming_quant_input(torch.empty((3, 5, 512), dtype=torch.bfloat16, device=dev), "float8e4m3")
+        assert tuple(q.shape) == (3, 5, 512) and q.dtype == torch.float8_e4m3fn
+        assert tuple(s.shape) == (15, 1) and s.dtype == torch.float32
+        with pytest.raises(NotImplementedError):
+            torch.ops.humming.humming_quant_input(torch.empty((4, 512), dtype=torch.bfloat16, device=dev), "int8")
+        with pytest.raises(NotImplementedError):
+            torch.ops.humming.humming_quant_input(torch.empty((4, 512), dtype=torch.bfloat16, device=dev), "float8e4m3",
+                                                  None, 128)
+    finally:
+        if mode:
+            mode.__exit__(None, None, None)
+
+
+def test_no_cpu_implementation():
+    dense = ops.desc_to_configs(runtime.make_desc(1024, 512, "float16", "uint4", "float16", "float16", group_size=128))
+    with pytest.raises(NotImplementedError, match="CPU"):
+        _launch(dense, torch.zeros((4, 512), dtype=torch.float16), locks=torch.zeros(64, dtype=torch.uint8))
+    with pytest.raises(NotImplementedError, match="CPU"):
+        torch.ops.humming.humming_quant_input(torch.zeros((4, 512), dtype=torch.bfloat16), "float8e4m3")
+
+
+def test_layer_configs_carry_the_layers_options():
+    layer = HummingLayer(shape_n=256, shape_k=512, a_dtype="bfloat16", b_dtype="uint4", c_dtype="bfloat16",
+                         bs_dtype="bfloat16", weight_scale_group_size=128, has_dynamic_zp=True, num_experts=16)
+    HummingMethod.prepare_default_kernel_configs(layer, is_moe=True, top_k=4, is_moe_down=True)
+    configs = ops.layer_configs(layer)
+    for tokens in (1, 64, 65, 200, 5000):
+        desc = ops.configs_to_desc(configs, tokens)
+        assert desc.m_tile == HummingMethod.moe_block_size(layer, tokens)
+        assert (desc.shape_n, desc.shape_k, desc.num_experts, desc.top_k, desc.is_moe_down, desc.has_zp) == (256, 512, 16, 4, 1, 1)
+    dense = HummingLayer(shape_n=256, shape_k=512, a_dtype="float16", b_dtype="uint4", c_dtype="float16",
+                         bs_dtype="float16", weight_scale_group_size=128)
+    HummingMethod.prepare_default_kernel_configs(dense, use_stream_k=False)
+    HummingMethod.add_kernel_config(dense, 1, 8, (16, 128, 128))
+    desc = ops.configs_to_desc(ops.layer_configs(dense), 4)
+    assert desc.m_tile == 16 and desc.flags & native.HM_FLAG_NO_SPLIT_K
+    assert ops.configs_to_desc(ops.layer_configs(dense), 9).m_tile == 0

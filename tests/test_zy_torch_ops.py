@@ -1,0 +1,101 @@
+"""GPU parity of the operator-level surface: ``torch.ops.humming.launch_humming`` and
+``torch.ops.humming.humming_quant_input`` must produce exactly what ``HummingLayer.forward`` produces for the
+same tensors (both end in the same C-ABI call), which the other GPU tests compare against the CPU oracle.
+Collected late so that a failure here does not hide the layer-level parity tests."""
+import pytest
+import torch
+
+from helpers import ATOL_16, RTOL_16, build_layer, oracle, oracle_weight
+from humming_b200 import ops, runtime
+from humming_b200.layer import HummingLayer, HummingMethod
+from humming_b200.utils import synthetic
+
+pytestmark = pytest.mark.gpu
+
+
+def _fresh_workspace(configs, m, device, capacity=None):
+    return torch.zeros(max(ops.workspace_bytes(configs, m, capacity), 1 << 16), dtype=torch.uint8, device=device)
+
+
+@pytest.mark.parametrize("m", [1, 16, 300])
+def test_launch_humming_dense_equals_forward(cuda_device, m):
+    case = synthetic.dense_w4a16_case(1024, 2048, torch.bfloat16, True, seed=51)
+    layer, _ = build_layer(case)
+    x = synthetic.activations(m, 2048, torch.bfloat16, seed=60 + m).to(cuda_device)
+    want = layer(inputs=x).clone()
+    layer.check_status()
+    ref = oracle.gemm_ref(x.float().cpu(), torch.from_numpy(oracle_weight(case)), torch.bfloat16)
+    torch.testing.assert_close(want.float().cpu(), ref.float(), atol=ATOL_16, rtol=RTOL_16)
+
+    configs = ops.layer_configs(layer)
+    locks = _fresh_workspace(configs, m, cuda_device)
+    got = torch.ops.humming.launch_humming(configs, x, layer.weight, None, None, layer.weight_scale, layer.zero_point,
+                                           None, None, None, None, None, None, locks)
+    assert got.shape == want.shape and got.dtype == want.dtype
+    assert torch.equal(got, want)
+    # into a caller's tensor, a batched view of the same rows, the workspace reused as it was left
+    given = torch.empty((1, m, 1024), dtype=torch.bfloat16, device=cuda_device)
+    back = torch.ops.humming.launch_humming(configs, x.view(1, m, 2048), layer.weight, given, None, layer.weight_scale,
+                                            layer.zero_point, None, None, None, None, None, None, locks)
+    assert back.data_ptr() == given.data_ptr() and torch.equal(given.view(m, 1024), want)
+    runtime.check_status(locks)
+    with pytest.raises(ValueError):   # no workspace: refused, nothing is allocated behind the caller's back
+        torch.ops.humming.launch_humming(configs, x, layer.weight, None, None, layer.weight_scale, layer.zero_point,
+                                         None, None, None, None, None, None, None)
+    with pytest.raises(ValueError):   # K does not match the descriptor
+        torch.ops.humming.launch_humming(configs, x[:, :1024].contiguous(), layer.weight, None, None, layer.weight_scale,
+                                         layer.zero_point, None, None, None, None, None, None, locks)
+
+
+@pytest.mark.parametrize("is_down", [False, True])
+def test_launch_humming_moe_equals_forward(cuda_device, is_down):
+    from test_gpu_moe import make_moe_layer
+
+    m, e, top_k = 50, 8, 2
+    layer, _ = make_moe_layer(e, 512, 1024, torch.bfloat16, True, cuda_device, top_k, is_down, seed=77)
+    gen = torch.Generator(device="cpu").manual_seed(3)
+    topk_weights, topk_ids = torch.randn((m, e), generator=gen).topk(top_k, 1)
+    x = torch.randn((m * (top_k if is_down else 1), 1024), generator=gen).bfloat16().to(cuda_device)
+    inputs = x.view(m, top_k, -1) if is_down else x
+    block = HummingMethod.moe_block_size(layer, m)
+    sorted_ids, expert_ids, total = runtime.moe_align_block_size(topk_ids.int().to(cuda_device), e, block)
+    tkw = topk_weights.to(cuda_device)
+    want = layer(inputs=inputs, topk_weights=tkw, sorted_token_ids=sorted_ids, expert_ids=expert_ids,
+                 num_tokens_post_padded=total).clone()
+    layer.check_status()
+
+    configs = ops.layer_configs(layer)
+    locks = _fresh_workspace(configs, m, cuda_device, capacity=sorted_ids.numel())
+    got = torch.ops.humming.launch_humming(configs, inputs, layer.weight, None, None, layer.weight_scale, layer.zero_point,
+                                           None, None, tkw, sorted_ids, expert_ids, total, locks)
+    runtime.check_status(locks)
+    assert tuple(got.shape) == (m, top_k, 512)
+    assert torch.equal(got, want)
+
+
+def test_quant_input_and_fp8_launch_equal_forward(cuda_device):
+    m, n, k = 40, 512, 1024
+    gen = torch.Generator(device="cpu").manual_seed(5)
+    codes = torch.randint(0, 16, (n, k), generator=gen, dtype=torch.int32)
+    scales = (torch.randn((n, k // 128), generator=gen).abs() * 0.02 + 1e-3).bfloat16()
+    layer = HummingLayer(shape_n=n, shape_k=k, a_dtype="float8e4m3", b_dtype="uint4", c_dtype="bfloat16",
+                         bs_dtype="bfloat16", weight_scale_group_size=128).to(cuda_device)
+    layer.load_weight(weight=codes.to(cuda_device), weight_scale=scales.to(cuda_device))
+    layer.finish_load()
+    x = torch.randn((m, k), generator=gen).bfloat16().to(cuda_device)
+
+    q, s = torch.ops.humming.humming_quant_input(x, "float8e4m3")
+    q_want, s_want = runtime.quant_input(x, "float8e4m3")
+    assert q.dtype == torch.float8_e4m3fn and tuple(s.shape) == (m, 1) and s.dtype == torch.float32
+    assert torch.equal(q.view(torch.uint8), q_want.view(torch.uint8)) and torch.equal(s, s_want.reshape(-1, 1))
+    _, s_cpu = oracle.quant_input_e4m3(x.cpu())
+    assert torch.equal(s.cpu(), s_cpu.reshape(-1, 1))
+
+    want = layer(inputs=q, input_scale=s).clone()
+    layer.check_status()
+    configs = ops.layer_configs(layer)
+    locks = _fresh_workspace(configs, m, cuda_device)
+    got = torch.ops.humming.launch_humming(configs, q, layer.weight, None, s, layer.weight_scale, None, None, None,
+                                           None, None, None, None, locks)
+    runtime.check_status(locks)
+    assert torch.equal(got, want)

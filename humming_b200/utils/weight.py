@@ -61,7 +61,8 @@ def quantize_weight(
         # quant_weight.cuh:205-214: the larger-magnitude side is mapped to -2^(b-1).
         max_abs = torch.maximum(max_val, min_val.abs())
         min_abs = torch.minimum(max_val, min_val.abs())
-        scale = torch.maximum(max_abs / (dmax + 1.499), min_abs / (dmax + 0.499))
+        # double divisions rounded to fp32 once, as the kernel's `dtype_max_val + 1.499` (a double literal) makes them
+        scale = torch.maximum((max_abs.double() / (dmax + 1.499)).float(), (min_abs.double() / (dmax + 0.499)).float())
         scale = torch.where(max_val > min_val.abs(), -scale, scale)
         zero_point = None
         inv = 1.0 / scale

@@ -13,3 +13,8 @@ g++ -O2 -fno-strict-aliasing -std=c++17 -shared -fPIC -Wno-unknown-pragmas -Wno-
     -I"$HERE/ref_shim" -I"$REF/humming/include" -I"$CUDA_INC" \
     -o "$HERE/_ref/libhumming_ref_host.so" "$HERE/ref_host.cpp"
 echo "$HERE/_ref/libhumming_ref_host.so"
+# The cooperative weight quantizer (quant_weight.cuh), run by 32 host threads: see ref_host_quant.cpp.
+g++ -O2 -fno-strict-aliasing -std=c++17 -shared -fPIC -pthread -Wno-unknown-pragmas -Wno-attributes \
+    -I"$HERE/ref_shim" -I"$REF/humming/include" -I"$CUDA_INC" \
+    -o "$HERE/_ref/libhumming_ref_host_quant.so" "$HERE/ref_host_quant.cpp"
+echo "$HERE/_ref/libhumming_ref_host_quant.so"

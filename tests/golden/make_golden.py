@@ -12,6 +12,14 @@ What is executed from the reference, unmodified:
   * pack_weight_kernel / unpack_weight_kernel / dequant_unpacked_fp_type,
     the reference's CUDA kernel bodies compiled for the host
     (oracle/ref_host.cpp)                                       -> pack_bits.npz, decode_fp.npz
+  * humming.kernel.quant_input._quant_tensor_kernel, the reference's Triton
+    kernel, run by Triton's CPU interpreter (TRITON_INTERPRET=1)  -> quant_input.npz
+    Only the per-token scales are kept: the interpreter's float32 -> e4m3 cast
+    is not the hardware's (it drops the carry out of the mantissa and rounds
+    ties up), so the codes it writes say nothing about the GPU kernel.
+  * quant_weight (humming/include/humming/kernel/quant_weight.cuh), the
+    reference's cooperative quantizer kernel run by 32 host threads
+    (oracle/ref_host_quant.cpp)                                   -> quant_weight.npz
 The reference has no fixtures of its own; these files are the pinned vectors
 the CPU oracle is checked against wherever the reference tree is absent.
 """
@@ -19,6 +27,8 @@ import ctypes
 import json
 import os
 import sys
+
+os.environ.setdefault("TRITON_INTERPRET", "1")   # before anything imports triton
 from unittest import mock
 
 import numpy as np
@@ -112,7 +122,61 @@ def golden_host_kernels():
     np.savez_compressed(os.path.join(HERE, "decode_fp.npz"), **dec)
 
 
+QUANT_WEIGHT_CASES = [(4, 0, 128, 0), (4, 0, 128, 1), (4, 0, 32, 0), (4, 0, 32, 1), (8, 0, 128, 0), (8, 0, 128, 1),
+                      (4, 1, 128, 0), (8, 1, 128, 0)]          # (bits, signed, group size, dynamic zero point)
+
+
+def golden_quant_weight():
+    lib = ctypes.CDLL(os.path.join(ROOT, "oracle", "_ref", "libhumming_ref_host_quant.so"))
+    ptr = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+    rng = np.random.default_rng(77)
+    out = {}
+    for i, (bits, signed, g, zp) in enumerate(QUANT_WEIGHT_CASES):
+        w = (rng.standard_normal((8, 256)) * 0.05).astype(np.float32)
+        w[1, :g] = 0                                    # an all-zero group: the +-1e-30 floors
+        w[2, :g] = np.abs(w[2, :g])                     # one-sided groups
+        w[3, g:2 * g] = -np.abs(w[3, g:2 * g])
+        groups = w.size // g
+        codes = np.zeros(w.size, np.int32)
+        scales = np.zeros(groups, np.float32)
+        zps = np.zeros(groups, np.uint32)
+        assert lib.ref_quant_weight_f32(ptr(w), ptr(codes), ptr(scales), ptr(zps), ctypes.c_long(groups), g, bits, signed, zp) == 0
+        out[f"c{i}_cfg"] = np.array([bits, signed, g, zp])
+        out[f"c{i}_w"] = w
+        out[f"c{i}_codes"] = codes.reshape(w.shape)
+        out[f"c{i}_scales"] = scales.reshape(8, -1)
+        if zp:
+            out[f"c{i}_zero_points"] = zps.astype(np.int32).reshape(8, -1)
+    np.savez_compressed(os.path.join(HERE, "quant_weight.npz"), **out)
+
+
+def golden_quant_input():
+    import importlib.util
+
+    import triton
+
+    spec = importlib.util.spec_from_file_location("ref_quant_input", os.path.join(REF, "humming", "kernel", "quant_input.py"))
+    ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref)
+    out = {}
+    for i, (dtype, m, k) in enumerate([(torch.bfloat16, 5, 256), (torch.float16, 4, 1000), (torch.float32, 3, 4096),
+                                       (torch.bfloat16, 2, 7168)]):
+        gen = torch.Generator(device="cpu").manual_seed(300 + i)
+        x = (torch.randn((m, k), generator=gen) * (3.0 if i % 2 else 1.0)).to(dtype)
+        x[1].zero_()                                  # an all-zero token: the 1e-30 floor of the scale
+        q = torch.empty((m, k), dtype=torch.float8_e4m3fn)
+        scale = torch.empty((m, 1), dtype=torch.float32)
+        ref._quant_tensor_kernel[(m,)](x, q, scale, x.stride(0), True, k, k, triton.next_power_of_2(k), "float8e4m3",
+                                       num_warps=1, num_stages=1)
+        out[f"c{i}_dtype"] = np.array(str(dtype))
+        out[f"c{i}_x_bits"] = x.view(torch.int32 if dtype == torch.float32 else torch.int16).numpy()
+        out[f"c{i}_scale"] = scale.numpy()
+    np.savez_compressed(os.path.join(HERE, "quant_input.npz"), **out)
+
+
 if __name__ == "__main__":
+    golden_quant_input()
+    golden_quant_weight()
     golden_dtypes()
     golden_host_kernels()
     golden_moe_align()

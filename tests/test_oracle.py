@@ -104,6 +104,67 @@ def test_quantize_weight_round_trip_error_bound(zp):
     assert np.all(np.abs(ref - w) <= 0.5001 * step + 1e-6)
 
 
+def _quant_weight_cases():
+    g = np.load(os.path.join(GOLD, "quant_weight.npz"))
+    for i in range(8):
+        bits, signed, group, zp = (int(v) for v in g[f"c{i}_cfg"])
+        yield bits, signed, group, zp, g[f"c{i}_w"], g[f"c{i}_codes"], g[f"c{i}_scales"], (g[f"c{i}_zero_points"] if zp else None)
+
+
+def test_quantize_weight_matches_the_reference_kernel_golden():
+    """Codes, fp32 scales and zero points written by the reference's quant_weight kernel (run on the host when the
+    fixture was made), bit for bit: uint4 / int4 / uint8 / int8, groups of 128 and 32, with and without zero points,
+    including all-zero and one-sided groups."""
+    for bits, signed, group, zp, w, codes, scales, zps in _quant_weight_cases():
+        q, s, z = oracle.quantize_weight_int(w, bits, group, bool(zp))
+        if signed:
+            q = q - 2 ** (bits - 1)        # the kernel adds the offset for unsigned targets only
+        assert np.array_equal(q, codes), (bits, signed, group, zp)
+        assert np.array_equal(s.view(np.uint32), scales.view(np.uint32)), (bits, signed, group, zp)
+        if zp:
+            assert np.array_equal(z, zps)
+
+
+def test_library_quantize_weight_matches_the_reference_kernel_golden():
+    """The torch restatement the layer uses for float checkpoints (humming_b200.utils.weight.quantize_weight)
+    against the same vectors (unsigned targets: the library takes the unsigned counterpart, as the reference's
+    generators do)."""
+    from humming_b200.utils.weight import quantize_weight
+
+    for bits, signed, group, zp, w, codes, scales, zps in _quant_weight_cases():
+        if signed:
+            continue
+        q, s, z, _ = quantize_weight(torch.from_numpy(w), dtype=dtypes.DataType.from_str(f"uint{bits}"),
+                                     scale_dtype=dtypes.float32, group_size=group, has_dynamic_zp=bool(zp))
+        assert np.array_equal(q.numpy(), codes), (bits, group, zp)
+        assert np.array_equal(s.numpy().view(np.uint32), scales.view(np.uint32)), (bits, group, zp)
+        if zp:
+            assert np.array_equal(z.numpy(), zps)
+
+
+REF_QUANT_LIB = os.path.join(os.path.dirname(HERE), "oracle", "_ref", "libhumming_ref_host_quant.so")
+
+
+@pytest.mark.skipif(not os.path.exists(REF_QUANT_LIB), reason="oracle/_ref not built (needs the reference tree)")
+@pytest.mark.parametrize("bits,signed,group,zp", [(4, 0, 128, 0), (4, 0, 128, 1), (8, 1, 128, 0)])
+def test_quantize_weight_matches_reference_code(bits, signed, group, zp):
+    """Fresh random weights through the reference kernel itself (host build), not only the stored vectors."""
+    lib = ctypes.CDLL(REF_QUANT_LIB)
+    ptr = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+    rng = np.random.default_rng(bits * 100 + group + zp)
+    w = (rng.standard_normal((4, 512)) * rng.uniform(0.01, 3.0, size=(4, 1))).astype(np.float32)
+    groups = w.size // group
+    codes, scales, zps = np.zeros(w.size, np.int32), np.zeros(groups, np.float32), np.zeros(groups, np.uint32)
+    assert lib.ref_quant_weight_f32(ptr(w), ptr(codes), ptr(scales), ptr(zps), ctypes.c_long(groups), group, bits, signed, zp) == 0
+    q, s, z = oracle.quantize_weight_int(w, bits, group, bool(zp))
+    if signed:
+        q = q - 2 ** (bits - 1)
+    assert np.array_equal(q.reshape(-1), codes)
+    assert np.array_equal(s.reshape(-1).view(np.uint32), scales.view(np.uint32))
+    if zp:
+        assert np.array_equal(z.reshape(-1), zps.astype(np.int32))
+
+
 # ---------------------------------------------------------------- MoE alignment
 def test_moe_align_matches_golden():
     g = np.load(os.path.join(GOLD, "moe_align.npz"))
@@ -114,6 +175,24 @@ def test_moe_align_matches_golden():
         assert np.array_equal(expert_ids, g[f"c{i}_expert_ids"])
         assert int(total) == int(g[f"c{i}_num_tokens_post_padded"])
         assert sorted_ids.size % blk == 0 and (sorted_ids < m * k).sum() == m * k
+
+
+# ---------------------------------------------------------------- activation quantization
+def test_quant_input_scales_match_the_reference_triton_kernel():
+    """Per-token scales written by the reference's Triton kernel (run by Triton's CPU interpreter when the
+    fixture was made), bit for bit; one token of every case is all zero (the 1e-30 floor)."""
+    g = np.load(os.path.join(GOLD, "quant_input.npz"))
+    names = {"torch.bfloat16": torch.bfloat16, "torch.float16": torch.float16, "torch.float32": torch.float32}
+    for i in range(4):
+        dtype = names[str(g[f"c{i}_dtype"])]
+        x = torch.from_numpy(g[f"c{i}_x_bits"]).view(dtype)
+        q, scale = oracle.quant_input_e4m3(x)
+        want = g[f"c{i}_scale"]
+        assert np.array_equal(scale.numpy().view(np.uint32), want.view(np.uint32))
+        assert want[1, 0] == np.float32(1e-30) / np.float32(448.0)
+        # the codes decode, with the scale, to within half an e4m3 step of the input (7/8 of the top binade at most)
+        err = (q.float() * scale - x.float()).abs()
+        assert bool((err <= scale * 448.0 / 16.0 + 1e-30).all())
 
 
 # ---------------------------------------------------------------- host-side mirror of the reference interface

@@ -107,3 +107,30 @@ def test_layer_configs_carry_the_layers_options():
     desc = ops.configs_to_desc(ops.layer_configs(dense), 4)
     assert desc.m_tile == 16 and desc.flags & native.HM_FLAG_NO_SPLIT_K
     assert ops.configs_to_desc(ops.layer_configs(dense), 9).m_tile == 0
+
+
+def test_operator_traces_into_an_fx_graph_with_fake_tensors():
+    """What a tracing compiler needs from the operator: under fake tensors it records one call node with the output's
+    shape and dtype and launches nothing (no GPU is present when this runs)."""
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    from torch.fx.experimental.proxy_tensor import make_fx
+
+    configs = ops.desc_to_configs(runtime.make_desc(1024, 512, "bfloat16", "uint4", "bfloat16", "bfloat16", group_size=128,
+                                                    has_zp=True))
+
+    def block(x, w, s, z, locks):
+        y = torch.ops.humming.launch_humming(configs, x, w, None, None, s, z, None, None, None, None, None, None, locks)
+        return torch.nn.functional.silu(y)
+
+    with FakeTensorMode():
+        args = (torch.empty((7, 512), dtype=torch.bfloat16, device="cuda"),
+                torch.empty((32, 2048), dtype=torch.int32, device="cuda"),
+                torch.empty((4, 1024), dtype=torch.bfloat16, device="cuda"),
+                torch.empty((4, 128), dtype=torch.int32, device="cuda"),
+                torch.empty((1 << 16,), dtype=torch.uint8, device="cuda"))
+        graph = make_fx(block, tracing_mode="fake")(*args)
+    calls = [n for n in graph.graph.nodes if n.op == "call_function"]
+    assert [n.target for n in calls] == [torch.ops.humming.launch_humming.default, torch.ops.aten.silu.default]
+    val = calls[0].meta["val"]
+    assert tuple(val.shape) == (7, 1024) and val.dtype == torch.bfloat16 and val.device.type == "cuda"
+    assert list(calls[0].args[0]) == configs

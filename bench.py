@@ -223,10 +223,10 @@ def run_moe(args, rank, world, local_rank):
         # symmetric weights, e4m3 activations with per-token scales (quantized inside the layer, before both GEMMs);
         # bf16 group-128 weight scales (fp32 scales are not a combination the reference accepts either).
         experts, top_k, hidden, inter = 256, 8, 7168, 2048
-        moe = HummingMoE(hidden, inter, experts, top_k, b_dtype="int4", a_dtype="float8e4m3").to(dev)
+        moe = HummingMoE(hidden, inter, experts, top_k, b_dtype="int4", a_dtype="float8e4m3", ep_mode=args.ep_mode).to(dev)
     else:
         experts, top_k, hidden, inter = 128, 8, 2048, 768
-        moe = HummingMoE(hidden, inter, experts, top_k).to(dev)
+        moe = HummingMoE(hidden, inter, experts, top_k, ep_mode=args.ep_mode).to(dev)
     code_lo, code_hi = (-8, 8) if w4a8 else (0, 16)
     for local, e in enumerate(moe.ep.owned_experts()):
         gen = torch.Generator(device=dev).manual_seed(1000 + e)
@@ -243,10 +243,12 @@ def run_moe(args, rank, world, local_rank):
         gen = torch.Generator(device=dev).manual_seed(7 + rank)
         x = torch.randn((tokens, hidden), generator=gen, device=dev).bfloat16()
         logits = torch.randn((tokens, experts), generator=gen, device=dev)
+        # replicated tokens: every rank pads to the largest per-rank token count (known without communication)
+        pad_to = -(-total_tokens // world) if (world > 1 and args.ep_mode == "replicate") else None
+        step = lambda: moe(x, logits, pad_to=pad_to)
         for _ in range(max(args.warmup, 3)):
-            moe(x, logits)
+            step()
         moe.check_status()
-        step = lambda: moe(x, logits)
         if world == 1:
             # One GPU: no host-side step in the layer, so a forward is captured once and replayed.
             graph = torch.cuda.CUDAGraph()
@@ -283,9 +285,9 @@ def run_moe(args, rank, world, local_rank):
                                ("quantize, " if w4a8 else "") + "up GEMM, silu*mul, " + ("quantize, " if w4a8 else "") +
                                "down GEMM, top-k sum",
                    "experts": experts, "top_k": top_k, "hidden": hidden, "intermediate": inter, "tokens_total": top["tokens"],
-                   "parallelism": f"ep{world}" if world > 1 else "single GPU",
-                   "timing": "one GPU: CUDA graph of a forward replayed K times; expert parallel: eager (the exchange sizes are read on the host); "
-                             "CUDA events, max over ranks"},
+                   "parallelism": f"ep{world} ({args.ep_mode})" if world > 1 else "single GPU",
+                   "timing": "one GPU: CUDA graph of a forward replayed K times; expert parallel: eager launches (dispatch mode reads the "
+                             "exchange sizes on the host every step, replicate mode reads nothing); CUDA events, max over ranks"},
         "tflops": top["tokens_per_s"] * flops_per_token / 1e12,
         "sweep": results,
     }
@@ -570,6 +572,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="dense", choices=["dense", "moe", "moe-w4a8", "mxfp4"])
+    ap.add_argument("--ep-mode", default="dispatch", choices=["dispatch", "replicate"],
+                    help="moe workloads on more than one GPU: all-to-all dispatch / combine, or all-gather + reduce-scatter")
     ap.add_argument("--tokens", default=None, help="moe workload: total token counts to time, the last one is the headline")
     ap.add_argument("--native-flags", type=int, default=0, help="HM_FLAG_* bits OR-ed into every dense GEMM descriptor (kernel A/B comparisons)")
     ap.add_argument("--point", default=None, help="PROJ:M, e.g. gate_up:16 -- launch only this sweep point a few times")

@@ -18,6 +18,16 @@ source rank un-permutes and sums over top-k.  The exchange is data-dependent,
 so the split sizes travel first (one small all-to-all and a host read); id and
 weight ride in 8 extra bytes per row, so a layer needs three collectives
 (counts, dispatch, combine).
+
+A second mode, ``ep_mode="replicate"``, has no data-dependent shape and therefore
+no host read: every rank pads its tokens to a common count, one ``all_gather``
+brings all tokens with their routing to every rank, each rank computes only the
+entries routed to its own experts (the block alignment drops ids outside
+``[0, experts_per_rank)``), sums them over top-k per token, and one
+``reduce_scatter`` adds the partial sums of all ranks and hands every rank its own
+tokens.  It moves ``world`` times more activation bytes than dispatch, which pays
+while tokens * hidden stays small against the link bandwidth, and it is the
+variant for batches with fewer tokens than ranks.
 """
 from typing import Callable, List, Optional, Tuple
 
@@ -90,19 +100,64 @@ class ExpertParallel:
         return result.view(tokens, k, back.size(-1))
 
 
+    def forward_replicated(self, hidden: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor,
+                           experts_fn: Callable[[torch.Tensor, torch.Tensor, torch.Tensor], torch.Tensor],
+                           pad_to: Optional[int] = None) -> torch.Tensor:
+        """hidden (T, H); topk_ids / topk_weights (T, k) with global expert ids.  ``pad_to``: the common token count
+        every rank pads to (at least the largest T of any rank, the same value on all ranks; default T, for ranks
+        that hold equally many tokens).  ``experts_fn(rows (R, H), local_expert_ids (R, k), weights (R, k))`` returns
+        (R, H'): for every row the weighted sum over the entries whose id lies in ``[0, experts_per_rank)`` -- zero
+        where none does; ids outside that range belong to other ranks or to padding.  Returns (T, H'), already
+        summed over top-k.  No shape depends on the routing and nothing is read on the host."""
+        tokens, k = topk_ids.shape
+        if self.world == 1:
+            return experts_fn(hidden, topk_ids.int(), topk_weights.float())
+        rows_per_rank = tokens if pad_to is None else int(pad_to)
+        if tokens > rows_per_rank:
+            raise ValueError(f"{tokens} tokens do not fit pad_to={rows_per_rank}")
+        width, esz = hidden.size(1), hidden.element_size()
+        if (width * esz) % 4:
+            raise ValueError("hidden rows must be a multiple of four bytes")
+        extra = 8 * k // esz                      # k int32 ids and k fp32 weights behind every row
+        packed = hidden.new_zeros((rows_per_rank, width + extra))
+        packed[:tokens, :width] = hidden
+        meta = packed[:, width:].view(torch.int32)
+        meta[:, :k] = -1                          # padding rows route nowhere
+        meta[:tokens, :k] = topk_ids.int()
+        meta[:tokens, k:] = topk_weights.float().contiguous().view(torch.int32)
+        gathered = hidden.new_empty((self.world * rows_per_rank, width + extra))
+        dist.all_gather_into_tensor(gathered, packed, group=self.group)
+        g_meta = gathered[:, width:].view(torch.int32)
+        local_e = (g_meta[:, :k] - self.rank * self.experts_per_rank).contiguous()   # other ranks' ids fall out of range
+        weights = g_meta[:, k:].contiguous().view(torch.float32)
+        partial = experts_fn(gathered[:, :width].contiguous(), local_e, weights)
+        if dist.get_backend(self.group) == "nccl":
+            out = partial.new_empty((rows_per_rank, partial.size(-1)))
+            dist.reduce_scatter_tensor(out, partial.contiguous(), group=self.group)
+        else:                                     # gloo (the CPU tests) has no reduce-scatter
+            partial = partial.contiguous()
+            dist.all_reduce(partial, group=self.group)
+            out = partial[self.rank * rows_per_rank:(self.rank + 1) * rows_per_rank]
+        return out[:tokens]
+
+
 class HummingMoE(torch.nn.Module):
     """Quantized MoE layer (uint4 / int4 weights, 16-bit activations) built from
     two MoE ``HummingLayer``s holding this rank's experts."""
 
     def __init__(self, hidden_size: int, intermediate_size: int, num_experts: int, top_k: int, dtype: str = "bfloat16",
                  b_dtype: str = "uint4", weight_scale_group_size: int = 128, has_dynamic_zp: bool = False,
-                 group: Optional["dist.ProcessGroup"] = None, a_dtype: Optional[str] = None):
+                 group: Optional["dist.ProcessGroup"] = None, a_dtype: Optional[str] = None, ep_mode: str = "dispatch"):
         """``a_dtype="float8e4m3"`` selects W4A8: the hidden states and the SiLU*mul output are quantized per
         token (dynamic fp32 scales) before the up and the down GEMM; ``dtype`` stays the 16-bit type of scales,
-        intermediate results and outputs."""
+        intermediate results and outputs.  ``ep_mode`` (more than one rank only): ``"dispatch"`` sends every routed
+        entry to the rank of its expert, ``"replicate"`` gathers all tokens on every rank (module docstring)."""
         super().__init__()
         from humming_b200.layer import HummingLayer
 
+        if ep_mode not in ("dispatch", "replicate"):
+            raise ValueError(f"ep_mode must be 'dispatch' or 'replicate', got {ep_mode!r}")
+        self.ep_mode = ep_mode
         self.ep = ExpertParallel(num_experts, group)
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
         self.num_experts, self.top_k = num_experts, top_k
@@ -121,15 +176,27 @@ class HummingMoE(torch.nn.Module):
     def finish_load(self):
         from humming_b200.layer import HummingMethod
 
-        # Rows reaching the experts through dispatch are one "token" each (top_k = 1);
-        # on a single GPU the GEMMs index the un-duplicated hidden states directly.
-        k = self.top_k if self.ep.world == 1 else 1
+        # Rows reaching the experts through dispatch are one "token" each (top_k = 1); on a single
+        # GPU and with replicated tokens the GEMMs index the un-duplicated hidden states directly.
+        k = self.top_k if (self.ep.world == 1 or self.ep_mode == "replicate") else 1
         for layer, down in ((self.up, False), (self.down, True)):
             HummingMethod.finish_load(layer)
             HummingMethod.prepare_default_kernel_configs(layer, is_moe=True, top_k=k, is_moe_down=down)
+            if self.ep.world > 1 and self.ep_mode == "replicate":
+                # The token tile follows the rows one expert gets.  With replicated tokens a rank sees every token
+                # but only the entries of its own experts, so the table is keyed as if all experts were here.
+                table, lo = [], 0
+                for block in (16, 32, 64):
+                    hi = max(lo, block * self.num_experts // k)
+                    table += [lo, hi, block]
+                    lo = hi + 1
+                layer.humming_block_size_configs[""] = table + [lo, 1 << 31, 128]
 
-    def _experts(self, rows: torch.Tensor, local_e: torch.Tensor, w: torch.Tensor, top_k: int) -> torch.Tensor:
-        """rows (T, H) with T*top_k routed entries (local_e, w flat) -> weighted outputs (T*top_k, H)."""
+    def _experts(self, rows: torch.Tensor, local_e: torch.Tensor, w: torch.Tensor, top_k: int,
+                 partial: bool = False) -> torch.Tensor:
+        """rows (T, H) with T*top_k routed entries (local_e, w flat) -> weighted outputs (T*top_k, H).
+        ``partial``: some entries carry ids outside ``[0, experts_per_rank)`` (other ranks' experts, padding); they
+        are left out of the alignment, so nothing computes or writes their rows: the output starts from zero."""
         from humming_b200 import runtime
         from humming_b200.layer import HummingMethod
 
@@ -150,13 +217,27 @@ class HummingMoE(torch.nn.Module):
         act_scale = None
         if self.fp8:
             act, act_scale = runtime.quant_input(act, "float8e4m3")
-        out = self.down(inputs=act, input_scale=act_scale, topk_weights=w, inputs_sorted=True, **routing)  # (T, k, H)
+        out = None
+        if partial:
+            out = torch.zeros((tokens, top_k, self.hidden_size), dtype=h.dtype, device=h.device)
+        out = self.down(inputs=act, input_scale=act_scale, topk_weights=w, inputs_sorted=True, outputs=out, **routing)  # (T, k, H)
         return out.view(tokens * top_k, self.hidden_size)
 
-    def forward(self, hidden_states: torch.Tensor, router_logits: torch.Tensor) -> torch.Tensor:
+    def _experts_partial(self, rows: torch.Tensor, local_e: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """Replicated tokens: rows (R, H), ids / weights (R, k) -> (R, H) summed over the local entries of each row."""
+        from humming_b200 import runtime
+
+        per_slot = self._experts(rows, local_e.reshape(-1), w.reshape(-1), self.top_k, partial=True)
+        return runtime.topk_sum(per_slot.view(rows.size(0), self.top_k, self.hidden_size))
+
+    def forward(self, hidden_states: torch.Tensor, router_logits: torch.Tensor, pad_to: Optional[int] = None) -> torch.Tensor:
+        """``pad_to`` (``ep_mode="replicate"`` only): the common token count of all ranks, see
+        ``ExpertParallel.forward_replicated``."""
         from humming_b200 import runtime
 
         topk_ids, topk_w = runtime.moe_route(router_logits, self.top_k, use_softmax=True, renormalize=True)
+        if self.ep.world > 1 and self.ep_mode == "replicate":
+            return self.ep.forward_replicated(hidden_states, topk_ids, topk_w, self._experts_partial, pad_to)
         if self.ep.world == 1:
             per_slot = self._experts(hidden_states, topk_ids.view(-1), topk_w.view(-1), self.top_k)
             per_slot = per_slot.view(hidden_states.size(0), self.top_k, self.hidden_size)

@@ -126,3 +126,60 @@ def test_single_rank_path_needs_no_process_group():
         return torch.stack([w[i] * (rows[i] @ weights[int(e[i])]) for i in range(rows.size(0))])
 
     torch.testing.assert_close(ep.forward(hidden, ids.int(), wts, experts_fn), _reference(hidden, ids, wts, weights))
+
+
+# ---------------------------------------------------------------- replicated tokens (no data-dependent shapes)
+def _worker_replicated(rank, world, port, outdir, tokens_of, dtype_name):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        dtype = getattr(torch, dtype_name)
+        gen = torch.Generator().manual_seed(0)
+        weights = torch.randn((E, H, H), generator=gen)
+        gen_r = torch.Generator().manual_seed(20 + rank)
+        tokens = tokens_of[rank]
+        hidden = torch.randn((tokens, H), generator=gen_r).to(dtype)
+        logits = torch.randn((tokens, E), generator=gen_r)
+        wts, ids = torch.softmax(logits, -1).topk(K, 1)
+        ep = ExpertParallel(E)
+        per = ep.experts_per_rank
+        seen = {"local": 0}
+
+        def experts_fn(rows, local_e, w):
+            assert rows.shape == (world * max(tokens_of), H) and local_e.shape == w.shape == (rows.size(0), K)
+            out = torch.zeros((rows.size(0), H))
+            for i in range(rows.size(0)):
+                for j in range(K):
+                    e = int(local_e[i, j])
+                    if 0 <= e < per:
+                        seen["local"] += 1
+                        out[i] += w[i, j] * (rows[i].float() @ weights[rank * per + e])
+            return out.to(rows.dtype)
+
+        got = ep.forward_replicated(hidden, ids.int(), wts, experts_fn, pad_to=max(tokens_of))
+        assert got.shape == (tokens, H) and got.dtype == dtype
+        want = torch.zeros((tokens, H))
+        for t in range(tokens):
+            for j in range(K):
+                want[t] += wts[t, j] * (hidden[t].float() @ weights[ids[t, j]])
+        tol = 1e-5 if dtype == torch.float32 else 5e-2
+        torch.testing.assert_close(got.float(), want, rtol=tol, atol=tol)
+        # every routed entry was computed exactly once, on the rank of its expert; padding rows nowhere
+        total = torch.tensor([seen["local"]])
+        dist.all_reduce(total)
+        assert int(total) == sum(tokens_of) * K
+        open(os.path.join(outdir, f"ok{rank}"), "w").close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_replicated_tokens_two_ranks_ragged(tmp_path):
+    mp.spawn(_worker_replicated, args=(2, _free_port(), str(tmp_path), (5, 9), "float32"), nprocs=2, join=True)
+    assert sorted(os.listdir(tmp_path)) == ["ok0", "ok1"]
+
+
+def test_replicated_tokens_four_ranks_one_token(tmp_path):
+    """Fewer tokens than ranks, 16-bit rows (ids and weights ride behind each row in 8 * k extra bytes)."""
+    mp.spawn(_worker_replicated, args=(4, _free_port(), str(tmp_path), (1, 0, 0, 0), "bfloat16"), nprocs=4, join=True)
+    assert sorted(os.listdir(tmp_path)) == ["ok0", "ok1", "ok2", "ok3"]

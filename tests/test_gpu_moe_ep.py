@@ -21,7 +21,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, outdir):
+def _worker(rank, world, port, outdir, ep_mode="dispatch"):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
@@ -30,14 +30,16 @@ def _worker(rank, world, port, outdir):
 
         dev = torch.device("cuda", rank)
         weights = make_expert_weights(EXPERTS, HIDDEN, INTER, seed=3)
-        moe = HummingMoE(HIDDEN, INTER, EXPERTS, TOP_K).to(dev)
+        moe = HummingMoE(HIDDEN, INTER, EXPERTS, TOP_K, ep_mode=ep_mode).to(dev)
         for local, e in enumerate(moe.ep.owned_experts()):
             moe.load_expert(local, weights[0][e].to(dev), weights[1][e].to(dev), weights[2][e].to(dev), weights[3][e].to(dev))
         moe.finish_load()
         gen = torch.Generator(device="cpu").manual_seed(100 + rank)
         x = torch.randn((TOKENS + 7 * rank, HIDDEN), generator=gen).bfloat16()
         logits = torch.randn((TOKENS + 7 * rank, EXPERTS), generator=gen)
-        out = moe(x.to(dev), logits.to(dev))
+        # ranks hold 40 and 47 tokens; the replicated mode pads both to the larger count
+        out = moe(x.to(dev), logits.to(dev), pad_to=TOKENS + 7 * (world - 1) if ep_mode == "replicate" else None)
+        assert out.shape == (TOKENS + 7 * rank, HIDDEN)
         moe.check_status()
         ref, _, _ = moe_layer_reference(x, logits, weights, TOP_K)
         torch.testing.assert_close(out.float().cpu(), ref.float(), rtol=0.05, atol=0.1)
@@ -47,6 +49,7 @@ def _worker(rank, world, port, outdir):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_expert_parallel_moe_two_gpus(tmp_path):
-    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+@pytest.mark.parametrize("ep_mode", ["dispatch", "replicate"])
+def test_expert_parallel_moe_two_gpus(tmp_path, ep_mode):
+    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path), ep_mode), nprocs=2, join=True)
     assert sorted(os.listdir(tmp_path)) == ["ok0", "ok1"]

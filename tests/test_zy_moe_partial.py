@@ -1,0 +1,56 @@
+"""GPU check of the building block of the replicated expert-parallel mode on one GPU: routed entries whose expert id
+lies outside ``[0, experts)`` (other ranks' experts, padding rows) are dropped by the block alignment, their output
+rows stay zero, and the sum over top-k holds only the local entries -- compared with a per-expert CPU loop that
+skips the same entries (bounds of the reference's MoE tests, tests/test_moe.py:104: rtol 0.05, atol 0.1)."""
+import pytest
+import torch
+
+from moe_common import dequant, make_expert_weights
+
+pytestmark = pytest.mark.gpu
+
+EXPERTS, TOP_K, HIDDEN, INTER = 8, 4, 512, 256
+
+
+def _reference(x, ids, wts, weights):
+    up_codes, up_scales, down_codes, down_scales = weights
+    out = torch.zeros((x.size(0), TOP_K, HIDDEN))
+    xf = x.float()
+    for e in range(EXPERTS):
+        tok, slot = torch.where(ids == e)
+        if tok.numel() == 0:
+            continue
+        wu, wd = dequant(up_codes[e], up_scales[e]), dequant(down_codes[e], down_scales[e])
+        h = (xf[tok] @ wu.T).bfloat16().float()
+        act = (torch.nn.functional.silu(h[:, :INTER]) * h[:, INTER:]).bfloat16().float()
+        out[tok, slot] = ((act @ wd.T) * wts[tok, slot, None]).bfloat16().float()
+    return out.sum(1)
+
+
+@pytest.mark.parametrize("tokens,keep", [(33, 0.5), (200, 0.125), (5, 0.0)])
+def test_entries_of_other_ranks_are_left_out(cuda_device, tokens, keep):
+    from humming_b200.moe import HummingMoE
+
+    weights = make_expert_weights(EXPERTS, HIDDEN, INTER, seed=11)
+    moe = HummingMoE(HIDDEN, INTER, EXPERTS, TOP_K).to(cuda_device)
+    for e in range(EXPERTS):
+        moe.load_expert(e, weights[0][e].to(cuda_device), weights[1][e].to(cuda_device), weights[2][e].to(cuda_device),
+                        weights[3][e].to(cuda_device))
+    moe.finish_load()
+    gen = torch.Generator(device="cpu").manual_seed(tokens)
+    x = torch.randn((tokens, HIDDEN), generator=gen).bfloat16()
+    wts, ids = torch.softmax(torch.randn((tokens, EXPERTS), generator=gen), -1).topk(TOP_K, 1)
+    ids = ids.int()
+    # entries that "belong to another rank": ids below zero, at and beyond the expert count
+    foreign = torch.rand((tokens, TOP_K), generator=gen) >= keep
+    ids[foreign] = torch.where(torch.rand((int(foreign.sum()),), generator=gen) < 0.5, -1 - ids[foreign], ids[foreign] + EXPERTS)
+    if keep == 0.0:
+        assert bool(((ids < 0) | (ids >= EXPERTS)).all())      # nothing local at all: the GEMMs find no tile
+
+    got = moe._experts_partial(x.to(cuda_device), ids.to(cuda_device), wts.to(cuda_device))
+    moe.check_status()
+    assert got.shape == (tokens, HIDDEN) and got.dtype == torch.bfloat16
+    want = _reference(x, ids, wts, weights)
+    torch.testing.assert_close(got.float().cpu(), want, rtol=0.05, atol=0.1)
+    untouched = ((ids < 0) | (ids >= EXPERTS)).all(1)
+    assert bool((got[untouched.to(cuda_device)] == 0).all())   # tokens without a local entry come out exactly zero

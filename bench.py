@@ -121,7 +121,8 @@ class ClockSampler:
 def cpu_reference_sample(sample_ms=(16, 256), threads=None, repeat=1):
     """The reference's CPU path on a bounded sample of the workload: for each of
     the four projections dequantise to fp32 ((q - zp) * s, timed) and run
-    torch.matmul for each M of `sample_ms`.  Returns (tflops, seconds, cores, text)."""
+    torch.matmul for each M of `sample_ms`.  Returns (tflops, seconds, cores, text); the text also gives the
+    split of the seconds into dequantisation and matmul."""
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import humming_oracle as oracle
     from humming_b200.utils import synthetic
@@ -130,18 +131,21 @@ def cpu_reference_sample(sample_ms=(16, 256), threads=None, repeat=1):
     torch.set_num_threads(cores)
     flops = 0.0
     secs = 0.0
+    dequant_secs = 0.0
     for _ in range(repeat):
         for _name, (n, k) in shapes():
             case = synthetic.dense_w4a16_case(n, k, torch.bfloat16, True, seed=0)
             xs = [synthetic.activations(m, k, torch.bfloat16).float() for m in sample_ms]
             t0 = time.perf_counter()
             w = case.weight_ref()  # fp32 dequant, torch CPU (reference humming/utils/test.py:109-128)
+            dequant_secs += time.perf_counter() - t0
             for m, x in zip(sample_ms, xs):
                 oracle.gemm_ref(x, w, torch.bfloat16)
                 flops += gemm_flops(m, n, k)
             secs += time.perf_counter() - t0
             del w, case
-    text = f"4 projections x M in {list(sample_ms)}: fp32 dequant + torch.matmul per projection, {repeat} pass(es)"
+    text = (f"4 projections x M in {list(sample_ms)}: fp32 dequant + torch.matmul per projection, {repeat} pass(es); "
+            f"{dequant_secs:.2f} s dequant + {secs - dequant_secs:.2f} s matmul")
     return flops / secs / 1e12, secs, cores, text
 
 

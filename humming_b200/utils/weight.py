@@ -109,6 +109,56 @@ def prepare_humming_weight(weight: torch.Tensor, b_dtype, a_dtype, zero_point=No
     return out if is_moe else out.squeeze(0)
 
 
+def _layout_desc(n: int, groups: int, scale_dtype, num_experts: int, has_zp: bool = False):
+    """A descriptor that fixes what the scale / zero-point layouts depend on: N, the number of groups along K
+    and the scale type.  (The group length itself does not enter: 32 for UE8M0 scales, 128 otherwise.)"""
+    g = 32 if scale_dtype == dtypes.float8e8m0 else 128
+    if scale_dtype == dtypes.float8e8m0:
+        return runtime.make_desc(shape_n=n, shape_k=groups * g, a_dtype=dtypes.float8e4m3, b_dtype=dtypes.float4e2m1,
+                                 c_dtype=dtypes.bfloat16, bs_dtype=scale_dtype, group_size=g, num_experts=num_experts)
+    return runtime.make_desc(shape_n=n, shape_k=groups * g, a_dtype=scale_dtype, b_dtype=dtypes.uint4, c_dtype=scale_dtype,
+                             bs_dtype=scale_dtype, group_size=g, has_zp=has_zp, num_experts=num_experts)
+
+
+def prepare_humming_weight_scale(weight_scale: torch.Tensor, to_apply_on_c: bool = False) -> torch.Tensor:
+    """Group scales (…, N, K/g) in fp16 / bf16 / UE8M0 -> the prepared scale buffer, shaped (…, K/g, N) like the
+    reference's (``humming/utils/weight.py:172-192``).  ``to_apply_on_c`` marks a tensor that is applied to the
+    output (a bias); those keep their natural order here, so only the transpose remains."""
+    if to_apply_on_c:
+        return weight_scale.transpose(-1, -2).contiguous()
+    is_moe = weight_scale.ndim == 3
+    s = (weight_scale if is_moe else weight_scale.unsqueeze(0)).contiguous()
+    e, n, groups = s.shape
+    desc = _layout_desc(n, groups, dtypes.DataType.from_torch_dtype(s.dtype), e if is_moe else 0)
+    out = runtime.repack_scale(desc, s).view(e, groups, n)
+    return out if is_moe else out.squeeze(0)
+
+
+def prepare_humming_zero_point(zero_point: Optional[torch.Tensor], dtype, packed: bool = False) -> Optional[torch.Tensor]:
+    """Zero-point codes (…, N, K/g) int32 of a weight type of at most four bits -> the prepared zero-point words,
+    shaped (-1, N / 8) like the reference's (``humming/utils/weight.py:195-216``)."""
+    if zero_point is None:
+        return None
+    if packed:
+        raise NotImplementedError("packed zero points are not built: pass the codes, one per int32")
+    if dtype.num_bits > 4:
+        raise NotImplementedError("zero points of weight types wider than four bits are not built")
+    is_moe = zero_point.ndim == 3
+    zp = (zero_point if is_moe else zero_point.unsqueeze(0)).contiguous()
+    e, n, groups = zp.shape
+    words = runtime.pack_weight(zp.view(e, -1), 4)
+    desc = _layout_desc(n, groups, dtypes.bfloat16, e if is_moe else 0, has_zp=True)
+    return runtime.repack_zero_point(desc, words).view(-1, n // 8)
+
+
+def prepare_humming_bias(bias: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    """The bias is read in its natural order by the epilogue (``humming/utils/weight.py:219-222`` permutes it
+    for the reference's fragment layout); returned unchanged, contiguous."""
+    if bias is None:
+        return None
+    return bias.contiguous()
+
+
 def prepare_humming_tensor_for_glu(tensor, shape_n: int, pad_shape_n: int = 0, is_moe: bool = False):
     """Interleave the two halves of the N rows (second half first) so that the
     pair a fused GLU epilogue combines sits in adjacent rows

@@ -99,3 +99,21 @@ def test_quant_input_and_fp8_launch_equal_forward(cuda_device):
                                            None, None, None, None, locks)
     runtime.check_status(locks)
     assert torch.equal(got, want)
+
+
+def test_prepare_helpers_give_what_finish_load_stores(cuda_device):
+    """``prepare_humming_weight_scale`` / ``prepare_humming_zero_point`` / ``prepare_humming_bias`` (the reference's
+    names, humming/utils/weight.py:172-222) produce the very bytes ``finish_load`` leaves in the parameters."""
+    from humming_b200 import dtypes
+    from humming_b200.utils.weight import prepare_humming_bias, prepare_humming_weight_scale, prepare_humming_zero_point
+
+    case = synthetic.dense_w4a16_case(512, 1024, torch.bfloat16, True, seed=71)
+    layer, bias = build_layer(case, has_bias=True)
+    scales = prepare_humming_weight_scale(case.scales.to(cuda_device))
+    assert tuple(scales.shape) == (1024 // 128, 512)
+    assert torch.equal(scales.reshape(-1).view(torch.int16), layer.weight_scale.data.reshape(-1).view(torch.int16))
+    zps = prepare_humming_zero_point(case.zero_points.to(cuda_device), dtypes.uint4)
+    assert zps.dtype == torch.int32 and zps.size(-1) == 512 // 8
+    assert torch.equal(zps.reshape(-1), layer.zero_point.data.reshape(-1))
+    assert torch.equal(prepare_humming_bias(bias.to(cuda_device)), layer.bias.data.reshape(-1))
+    assert prepare_humming_zero_point(None, dtypes.uint4) is None and prepare_humming_bias(None) is None

@@ -598,6 +598,9 @@ def main():
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        # The collectives here are a barrier, a two-float reduction and (MoE) point-to-point exchanges: none gains from
+        # in-switch reduction, so the NVLink multicast set-up is left out of communicator start-up.
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         import datetime
         # A collective that does not complete within five minutes ends the run with an error instead of hanging.
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=datetime.timedelta(minutes=5))

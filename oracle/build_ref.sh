@@ -1,6 +1,6 @@
 #!/bin/sh
 # Compiles oracle/ref_host.cpp against the reference's headers where they lie
-# (REF, default /root/reference) into oracle/_ref/libhumming_ref_host.so.
+# (the directory named by the variable REF) into oracle/_ref/libhumming_ref_host.so.
 # -fno-strict-aliasing: the kernels pun uint32 and float through pointers, which nvcc
 # tolerates and g++ -O2 otherwise miscompiles.
 # Only the checker uses it; nothing under oracle/_ref is committed.

@@ -1,6 +1,6 @@
 """Regenerates the golden fixtures in this directory from the reference itself.
 
-Run in a container where the reference tree is mounted (default /root/reference)
+Run in a container where the reference tree is mounted (its directory in the variable REF)
 and oracle/_ref has been built (sh oracle/build_ref.sh):
 
     python tests/golden/make_golden.py

@@ -164,3 +164,14 @@ def test_plan_pair_needs_256_row_multiples_and_flags_override():
     assert plan.cta_pair == 1 and plan.m_tile in (32, 64, 128)
     native.check(native.lib.hm_gemm_plan(_desc(shape_n=4096, shape_k=4096, num_sms=148, m_tile=192), 4096, plan))
     assert plan.cta_pair == 0 and plan.m_tile == 192              # the 192-token tile has no pair kernel
+
+
+@pytest.mark.parametrize("units_per_cta", [0, 1, 4])
+def test_schedule_of_an_moe_call_without_any_tile_is_empty(units_per_cta):
+    """An MoE launch whose routing leaves this GPU no entry (replicated tokens, nothing local) derives on the device
+    a schedule of zero tiles: every worker must find no segment (and divide by nothing)."""
+    plan = native.Plan()
+    plan.m_tile, plan.n_tiles, plan.m_tiles, plan.kb_per_tile = 16, 12, 0, 16
+    plan.mode, plan.grid, plan.units_per_cta, plan.total_units = 1, 148, units_per_cta, 0
+    for cta in (0, 1, 73, 147):
+        assert _segments(plan, cta) == []

@@ -5,6 +5,7 @@ skips the same entries (bounds of the reference's MoE tests, tests/test_moe.py:1
 import pytest
 import torch
 
+from helpers import oracle
 from moe_common import dequant, make_expert_weights
 
 pytestmark = pytest.mark.gpu
@@ -54,3 +55,25 @@ def test_entries_of_other_ranks_are_left_out(cuda_device, tokens, keep):
     torch.testing.assert_close(got.float().cpu(), want, rtol=0.05, atol=0.1)
     untouched = ((ids < 0) | (ids >= EXPERTS)).all(1)
     assert bool((got[untouched.to(cuda_device)] == 0).all())   # tokens without a local entry come out exactly zero
+
+
+@pytest.mark.parametrize("tokens,experts,top_k,block", [(33, 8, 4, 16), (700, 16, 8, 64), (3, 4, 2, 32)])
+def test_alignment_drops_ids_outside_the_expert_range(cuda_device, tokens, experts, top_k, block):
+    """No counterpart in the reference (its generator only produces valid ids): entries with an id below zero or at
+    and beyond the expert count appear nowhere in sorted_token_ids; the others are grouped by expert in rising id
+    order, each expert padded to the block with the sentinel, exactly as without the foreign entries."""
+    import numpy as np
+
+    from humming_b200 import runtime
+
+    gen = torch.Generator(device="cpu").manual_seed(tokens + experts)
+    ids = torch.randint(-experts, 2 * experts, (tokens, top_k), generator=gen, dtype=torch.int32)
+    sorted_ids, expert_ids, total = runtime.moe_align_block_size(ids.to(cuda_device), experts, block)
+    # the oracle's per-expert loop never sees an id outside [0, experts)
+    want_sorted, want_experts, want_total = oracle.moe_align_block_size(ids.numpy(), experts, block)
+    assert int(((ids >= 0) & (ids < experts)).sum()) < ids.numel()          # the case does hold foreign entries
+    t = int(total.item())
+    assert t == int(want_total)
+    assert np.array_equal(sorted_ids.cpu().numpy()[:t], want_sorted)
+    assert np.array_equal(expert_ids.cpu().numpy()[:t // block], want_experts)
+    assert bool((sorted_ids[t:] == ids.numel()).all())

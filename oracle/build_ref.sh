@@ -18,3 +18,9 @@ g++ -O2 -fno-strict-aliasing -std=c++17 -shared -fPIC -pthread -Wno-unknown-prag
     -I"$HERE/ref_shim" -I"$REF/humming/include" -I"$CUDA_INC" \
     -o "$HERE/_ref/libhumming_ref_host_quant.so" "$HERE/ref_host_quant.cpp"
 echo "$HERE/_ref/libhumming_ref_host_quant.so"
+# Register-level dequantization of the 16-bit paths (dequant_single.cuh) followed by the scale multiply: see
+# ref_host_dequant.cpp.
+g++ -O2 -fno-strict-aliasing -std=c++17 -shared -fPIC -Wno-unknown-pragmas -Wno-attributes \
+    -I"$HERE/ref_shim" -I"$REF/humming/include" -I"$CUDA_INC" \
+    -o "$HERE/_ref/libhumming_ref_host_dequant.so" "$HERE/ref_host_dequant.cpp"
+echo "$HERE/_ref/libhumming_ref_host_dequant.so"

@@ -20,6 +20,9 @@ What is executed from the reference, unmodified:
   * quant_weight (humming/include/humming/kernel/quant_weight.cuh), the
     reference's cooperative quantizer kernel run by 32 host threads
     (oracle/ref_host_quant.cpp)                                   -> quant_weight.npz
+  * dequant_single / dequant_single_zero_point (humming/include/humming/
+    datatype/dequant_single.cuh) followed by the 16-bit scale multiply, compiled
+    for the host (oracle/ref_host_dequant.cpp)                    -> dequant16.npz
 The reference has no fixtures of its own; these files are the pinned vectors
 the CPU oracle is checked against wherever the reference tree is absent.
 """
@@ -150,6 +153,30 @@ def golden_quant_weight():
     np.savez_compressed(os.path.join(HERE, "quant_weight.npz"), **out)
 
 
+def golden_dequant16():
+    lib = ctypes.CDLL(os.path.join(ROOT, "oracle", "_ref", "libhumming_ref_host_dequant.so"))
+    ptr = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+    rng = np.random.default_rng(16)
+    out = {}
+    n = 256
+    for bits in (2, 3, 4, 5, 6):
+        for is_bf16 in (0, 1):
+            for has_zp in (0, 1):
+                dtype = torch.bfloat16 if is_bf16 else torch.float16
+                q = rng.integers(0, 1 << bits, n, dtype=np.uint32)
+                zp = rng.integers(0, 1 << bits, n, dtype=np.uint32)
+                gen = torch.Generator().manual_seed(bits * 4 + is_bf16 * 2 + has_zp)
+                s = (torch.randn(n, generator=gen).abs() * 0.02 + 1e-3).to(dtype)
+                # a few scales at the ends of the range: results that overflow, that are subnormal, an exact zero
+                s[:6] = torch.tensor([1.0, 3e38 if is_bf16 else 65504.0, 1e-38 if is_bf16 else 6e-8, 0.0, 0.333, 2.0]).to(dtype)
+                s_bits = s.view(torch.int16).numpy().view(np.uint16).copy()
+                w_bits = np.zeros(n, np.uint16)
+                assert lib.ref_dequant_mul_16(ptr(q), ptr(zp), ptr(s_bits), ptr(w_bits), ctypes.c_long(n), bits, is_bf16, has_zp) == 0
+                key = f"b{bits}_{'bf16' if is_bf16 else 'f16'}_{'zp' if has_zp else 'sym'}"
+                out[key + "_q"], out[key + "_zp"], out[key + "_scale_bits"], out[key + "_w_bits"] = q, zp, s_bits, w_bits
+    np.savez_compressed(os.path.join(HERE, "dequant16.npz"), **out)
+
+
 def golden_quant_input():
     import importlib.util
 
@@ -177,6 +204,7 @@ def golden_quant_input():
 if __name__ == "__main__":
     golden_quant_input()
     golden_quant_weight()
+    golden_dequant16()
     golden_dtypes()
     golden_host_kernels()
     golden_moe_align()

@@ -93,6 +93,50 @@ def test_weight_ref_int_is_exact_and_matches_torch_expression():
     assert np.array_equal(eff, want.bfloat16().float().numpy())
 
 
+def _effective_16_bits(q, zp, scale_bits, bits, is_bf16, has_zp):
+    """The oracle's effective weight for one weight per 'group' (group size 1), as 16-bit patterns."""
+    dtype = torch.bfloat16 if is_bf16 else torch.float16
+    scale = torch.from_numpy(scale_bits.view(np.int16).copy()).view(dtype).float().numpy()
+    with np.errstate(over="ignore", invalid="ignore"):
+        w = oracle.weight_ref_int(q.reshape(1, -1).astype(np.int64), scale.reshape(1, -1), 1, bits,
+                                  zp.reshape(1, -1).astype(np.int64) if has_zp else None)
+        eff = oracle.effective_weight_16(w, "bfloat16" if is_bf16 else "float16").reshape(-1)
+    return torch.from_numpy(eff).to(dtype).view(torch.int16).numpy().view(np.uint16)
+
+
+def test_effective_16_bit_weight_matches_the_reference_dequant_golden():
+    """The 16-bit pattern the tensor cores multiply by -- the reference's dequant_single (exact q - zp through the
+    0x6400 / 0x4300 exponent trick) times the group scale in the same 16-bit type -- for uint2 ... uint6 codes, fp16 and
+    bf16, fixed and dynamic zero points, including scales whose products overflow, are subnormal or zero."""
+    g = np.load(os.path.join(GOLD, "dequant16.npz"))
+    for bits in (2, 3, 4, 5, 6):
+        for is_bf16 in (0, 1):
+            for has_zp in (0, 1):
+                key = f"b{bits}_{'bf16' if is_bf16 else 'f16'}_{'zp' if has_zp else 'sym'}"
+                got = _effective_16_bits(g[key + "_q"], g[key + "_zp"], g[key + "_scale_bits"], bits, is_bf16, has_zp)
+                assert np.array_equal(got, g[key + "_w_bits"]), key
+
+
+REF_DEQUANT_LIB = os.path.join(os.path.dirname(HERE), "oracle", "_ref", "libhumming_ref_host_dequant.so")
+
+
+@pytest.mark.skipif(not os.path.exists(REF_DEQUANT_LIB), reason="oracle/_ref not built (needs the reference tree)")
+@pytest.mark.parametrize("is_bf16,has_zp", [(0, 0), (0, 1), (1, 0), (1, 1)])
+def test_effective_16_bit_weight_matches_reference_code(is_bf16, has_zp):
+    """Every (code, zero point) pair of uint4 against a spread of scales, through the reference code itself."""
+    lib = ctypes.CDLL(REF_DEQUANT_LIB)
+    ptr = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+    dtype = torch.bfloat16 if is_bf16 else torch.float16
+    gen = torch.Generator().manual_seed(9)
+    scales = torch.cat([(torch.randn(62, generator=gen).abs() * 0.02 + 1e-3), torch.tensor([1.0, 0.75])]).to(dtype)
+    q, zp, s = np.meshgrid(np.arange(16, dtype=np.uint32), np.arange(16, dtype=np.uint32), np.arange(64), indexing="ij")
+    q, zp = np.ascontiguousarray(q.reshape(-1)), np.ascontiguousarray(zp.reshape(-1))
+    s_bits = scales.view(torch.int16).numpy().view(np.uint16)[s.reshape(-1)].copy()
+    w_bits = np.zeros(q.size, np.uint16)
+    assert lib.ref_dequant_mul_16(ptr(q), ptr(zp), ptr(s_bits), ptr(w_bits), ctypes.c_long(q.size), 4, is_bf16, has_zp) == 0
+    assert np.array_equal(_effective_16_bits(q, zp, s_bits, 4, is_bf16, has_zp), w_bits)
+
+
 @pytest.mark.parametrize("zp", [False, True])
 def test_quantize_weight_round_trip_error_bound(zp):
     rng = np.random.default_rng(5)

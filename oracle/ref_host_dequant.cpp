@@ -1,11 +1,12 @@
 // Test infrastructure, not product code.
 //
-// Runs the reference's register-level dequantization of 16-bit-activation GEMMs on the host CPU:
+// Runs the reference's register-level dequantization on the host CPU.  16-bit activations:
 // dequant_single<UIntN, Float16 | BFloat16, zero point?> and dequant_single_zero_point
 // (humming/include/humming/datatype/dequant_single.cuh), followed by the multiplication with the group scale in
 // the same 16-bit type that the main loop applies (humming/include/humming/arith/mainloop_arith.cuh:117-161,
 // __hmul2), so that the oracle's effective 16-bit weight, rn16(fp32(q - zp) * fp32(s)), can be pinned against the
-// reference's own code.  The header is included from where it lies (include path given by oracle/build_ref.sh);
+// reference's own code.  FP8 activations: dequant_single<Float4E2M1 | UInt4, Float8E4M3> (codes to e4m3 bit
+// patterns that are the weight times a fixed power of two) with get_dtype_dequant_exp_offset.  The header is included from where it lies (include path given by oracle/build_ref.sh);
 // its one inline-PTX helper, lop3_and_or (humming/include/humming/utils/ptx/logic.cuh: (a & b) | c as one lop3
 // instruction), is supplied here in plain C++, and the half-precision subtract / multiply are CUDA's own host
 // implementations from cuda_fp16.h / cuda_bf16.h.
@@ -19,6 +20,7 @@
 
 static inline uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t c) { return (a & b) | c; }
 
+#include <humming/arith/exp_offset.cuh>
 #include <humming/datatype/dequant_single.cuh>
 
 template <class Source, class Target, bool ZP>
@@ -49,7 +51,41 @@ static void run(const uint32_t* q, const uint32_t* zp, const uint16_t* scale, ui
   }
 }
 
+// FP8-activation paths: codes -> e4m3 bit patterns, four 8-bit lanes per word.
+template <int KIND>
+static uint32_t to_e4m3_word(uint32_t lanes, uint32_t zp) {
+  if constexpr (KIND == 0) return dequant_single<Float4E2M1, Float8E4M3, false>(lanes << 4, zp);  // code in the high nibble
+  if constexpr (KIND == 1) return dequant_single<UInt4, Float8E4M3, false>(lanes, zp);
+  return dequant_single<UInt4, Float8E4M3, true>(lanes, zp);
+}
+
 extern "C" {
+// kind 0: float4e2m1 codes; kind 1: uint4 codes, fixed zero point 8; kind 2: uint4 codes with a dynamic zero
+// point (one per call: the four lanes of a word share it, as the lanes of a fragment word share their group).
+// Integer codes are first rewritten the way the reference's repack kernel stores them for these paths
+// (humming/include/humming/kernel/process.cuh:207-219): v >= zp ? v - zp : 15 - v.
+// out: one e4m3 byte per code.  Returns the power-of-two exponent the reference folds back afterwards
+// (get_dtype_dequant_exp_offset, humming/include/humming/arith/exp_offset.cuh:8-36), or a negative error.
+int ref_dequant_to_e4m3(const uint32_t* q, uint32_t zp, uint8_t* out, long numel, int kind) {
+  if (numel % 4 || kind < 0 || kind > 2) return -2;
+  for (long i = 0; i < numel; i += 4) {
+    uint32_t lanes = 0;
+    for (int l = 0; l < 4; ++l) {
+      uint32_t v = q[i + l] & 15u;
+      if (kind != 0) {
+        const uint32_t z = kind == 1 ? 8u : zp;
+        v = v >= z ? v - z : 15u - v;
+      }
+      lanes |= v << (8 * l);
+    }
+    uint32_t w = kind == 0 ? to_e4m3_word<0>(lanes, zp) : (kind == 1 ? to_e4m3_word<1>(lanes, zp) : to_e4m3_word<2>(lanes, zp));
+    for (int l = 0; l < 4; ++l) out[i + l] = static_cast<uint8_t>(w >> (8 * l));
+  }
+  if (kind == 0) return static_cast<int>(get_dtype_dequant_exp_offset<Float8E4M3, Float4E2M1>());
+  if (kind == 1) return static_cast<int>(get_dtype_dequant_exp_offset<Float8E4M3, UInt4, false>());
+  return static_cast<int>(get_dtype_dequant_exp_offset<Float8E4M3, UInt4, true>());
+}
+
 // numel (even) codes of `bits` bits, zero points (ignored without has_zp) and 16-bit scale patterns, one per
 // weight -> the 16-bit pattern of the weight the tensor cores multiply by.
 int ref_dequant_mul_16(const uint32_t* q, const uint32_t* zp, const uint16_t* scale, uint16_t* out, long numel, int bits,

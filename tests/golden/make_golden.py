@@ -23,6 +23,8 @@ What is executed from the reference, unmodified:
   * dequant_single / dequant_single_zero_point (humming/include/humming/
     datatype/dequant_single.cuh) followed by the 16-bit scale multiply, compiled
     for the host (oracle/ref_host_dequant.cpp)                    -> dequant16.npz
+  * dequant_single<Float4E2M1 | UInt4, Float8E4M3> with the exponent offset of
+    get_dtype_dequant_exp_offset, same host build                 -> dequant_e4m3.npz
 The reference has no fixtures of its own; these files are the pinned vectors
 the CPU oracle is checked against wherever the reference tree is absent.
 """
@@ -177,6 +179,21 @@ def golden_dequant16():
     np.savez_compressed(os.path.join(HERE, "dequant16.npz"), **out)
 
 
+def golden_dequant_e4m3():
+    lib = ctypes.CDLL(os.path.join(ROOT, "oracle", "_ref", "libhumming_ref_host_dequant.so"))
+    ptr = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+    q = np.arange(16, dtype=np.uint32)
+    out = {}
+    for kind, zps in ((0, [0]), (1, [8]), (2, range(16))):     # float4e2m1; uint4 fixed zero point; uint4 dynamic zero point
+        for zp in zps:
+            bits = np.zeros(16, np.uint8)
+            off = lib.ref_dequant_to_e4m3(ptr(q), ctypes.c_uint32(zp), ptr(bits), ctypes.c_long(16), kind)
+            assert off >= 0
+            out[f"k{kind}_zp{zp}_bits"] = bits
+            out[f"k{kind}_zp{zp}_exp_offset"] = np.array(off)
+    np.savez_compressed(os.path.join(HERE, "dequant_e4m3.npz"), **out)
+
+
 def golden_quant_input():
     import importlib.util
 
@@ -205,6 +222,7 @@ if __name__ == "__main__":
     golden_quant_input()
     golden_quant_weight()
     golden_dequant16()
+    golden_dequant_e4m3()
     golden_dtypes()
     golden_host_kernels()
     golden_moe_align()

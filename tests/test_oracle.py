@@ -117,6 +117,21 @@ def test_effective_16_bit_weight_matches_the_reference_dequant_golden():
                 assert np.array_equal(got, g[key + "_w_bits"]), key
 
 
+def test_fp8_path_weight_codes_are_the_exact_weights_times_a_power_of_two():
+    """FP8-activation paths: the e4m3 patterns the reference's dequant_single produces from float4e2m1 codes and
+    from (rewritten) uint4 codes, decoded and multiplied by 2^offset (the exponent the reference folds back:
+    6 for e2m1, 9 for integers), are exactly the oracle's pre-scale weights: the e2m1 value, q - 8, q - zp."""
+    g = np.load(os.path.join(GOLD, "dequant_e4m3.npz"))
+    q = np.arange(16, dtype=np.uint32)
+    for kind, zps in ((0, [0]), (1, [8]), (2, range(16))):
+        for zp in zps:
+            off = int(g[f"k{kind}_zp{zp}_exp_offset"])
+            assert off == (6 if kind == 0 else 9)
+            got = oracle.decode_fp(g[f"k{kind}_zp{zp}_bits"].astype(np.uint32), 4, 3, True) * np.float32(2.0 ** off)
+            want = oracle.decode_fp(q, 2, 1, True) if kind == 0 else q.astype(np.float32) - np.float32(zp)
+            assert np.array_equal(got, want), (kind, zp)
+
+
 REF_DEQUANT_LIB = os.path.join(os.path.dirname(HERE), "oracle", "_ref", "libhumming_ref_host_dequant.so")
 
 

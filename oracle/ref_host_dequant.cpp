@@ -86,6 +86,14 @@ int ref_dequant_to_e4m3(const uint32_t* q, uint32_t zp, uint8_t* out, long numel
   return static_cast<int>(get_dtype_dequant_exp_offset<Float8E4M3, UInt4, true>());
 }
 
+// fp32 -> e4m3 with round-to-nearest-even and saturation to +-448, by CUDA's own host implementation of the
+// conversion (cuda_fp8.h, __nv_cvt_float_to_fp8): the instruction the reference's Triton quantizer compiles to
+// (tensor.to(tl.float8e4nv), humming/kernel/quant_input.py:36-37).  Checks the cast the oracle uses.
+int cuda_float_to_e4m3(const float* x, uint8_t* out, long numel) {
+  for (long i = 0; i < numel; ++i) out[i] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(x[i], __NV_SATFINITE, __NV_E4M3));
+  return 0;
+}
+
 // numel (even) codes of `bits` bits, zero points (ignored without has_zp) and 16-bit scale patterns, one per
 // weight -> the 16-bit pattern of the weight the tensor cores multiply by.
 int ref_dequant_mul_16(const uint32_t* q, const uint32_t* zp, const uint16_t* scale, uint16_t* out, long numel, int bits,

@@ -25,6 +25,9 @@ What is executed from the reference, unmodified:
     for the host (oracle/ref_host_dequant.cpp)                    -> dequant16.npz
   * dequant_single<Float4E2M1 | UInt4, Float8E4M3> with the exponent offset of
     get_dtype_dequant_exp_offset, same host build                 -> dequant_e4m3.npz
+Not reference code, but the definition of the instruction its Triton quantizer
+compiles to: CUDA's host implementation of the fp32 -> e4m3 conversion
+(cuda_fp8.h, round to nearest even, saturating), same host build  -> e4m3_cast.npz
 The reference has no fixtures of its own; these files are the pinned vectors
 the CPU oracle is checked against wherever the reference tree is absent.
 """
@@ -194,6 +197,21 @@ def golden_dequant_e4m3():
     np.savez_compressed(os.path.join(HERE, "dequant_e4m3.npz"), **out)
 
 
+def golden_e4m3_cast():
+    lib = ctypes.CDLL(os.path.join(ROOT, "oracle", "_ref", "libhumming_ref_host_dequant.so"))
+    ptr = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+    rng = np.random.default_rng(8)
+    codes = torch.arange(0, 127, dtype=torch.uint8).view(torch.float8_e4m3fn).float().numpy()
+    mids = ((codes[:-1] + codes[1:]) / 2).astype(np.float32)       # every tie between neighbouring e4m3 values
+    x = np.concatenate([mids, -mids, np.nextafter(mids, np.float32(0)), np.nextafter(mids, np.float32(1e9)),
+                        (rng.standard_normal(2000) * 100).astype(np.float32), (rng.standard_normal(2000) * 0.01).astype(np.float32),
+                        np.array([0.0, -0.0, 448.0, -448.0, 2.0 ** -9, 2.0 ** -10, 3 * 2.0 ** -10, 1e-30, 464.0, 1000.0, -1e9],
+                                 np.float32)]).astype(np.float32)
+    out = np.zeros(x.size, np.uint8)
+    assert lib.cuda_float_to_e4m3(ptr(x), ptr(out), ctypes.c_long(x.size)) == 0
+    np.savez_compressed(os.path.join(HERE, "e4m3_cast.npz"), x=x, codes=out)
+
+
 def golden_quant_input():
     import importlib.util
 
@@ -223,6 +241,7 @@ if __name__ == "__main__":
     golden_quant_weight()
     golden_dequant16()
     golden_dequant_e4m3()
+    golden_e4m3_cast()
     golden_dtypes()
     golden_host_kernels()
     golden_moe_align()

@@ -254,6 +254,22 @@ def test_quant_input_scales_match_the_reference_triton_kernel():
         assert bool((err <= scale * 448.0 / 16.0 + 1e-30).all())
 
 
+def test_e4m3_cast_of_the_oracle_is_the_saturating_round_to_nearest_even_conversion():
+    """The cast inside quant_input_e4m3 (clamp to +-448, torch's float8_e4m3fn conversion) against CUDA's host
+    implementation of cvt.rn.satfinite.e4m3 -- the instruction the reference's Triton kernel compiles to -- on every
+    tie between neighbouring e4m3 values, their fp32 neighbours, subnormals, values beyond the range and signed zeros."""
+    g = np.load(os.path.join(GOLD, "e4m3_cast.npz"))
+    x = torch.from_numpy(g["x"])
+    got = x.clamp(-448.0, 448.0).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    assert np.array_equal(got, g["codes"])
+    # and through the oracle function itself: a row whose largest magnitude is 448 has scale 1, so q is the bare cast
+    row = torch.cat([x[x.abs() <= 448.0], torch.tensor([448.0])]).reshape(1, -1)
+    q, scale = oracle.quant_input_e4m3(row)
+    assert float(scale) == 1.0
+    want = np.concatenate([g["codes"][(x.abs() <= 448.0).numpy()], np.array([0x7E], np.uint8)])
+    assert np.array_equal(q.view(torch.uint8).numpy().reshape(-1), want)
+
+
 # ---------------------------------------------------------------- host-side mirror of the reference interface
 def test_dtypes_match_reference_golden():
     gold = json.load(open(os.path.join(GOLD, "dtypes.json")))

@@ -9,6 +9,7 @@ What is executed from the reference, unmodified:
   * humming.dtypes (pure Python)                                -> dtypes.json
   * humming.utils.test.generate_random_moe_tensors, with torch's
     factory functions redirected from "cuda:0" to the CPU       -> moe_align.npz
+  * humming.utils.weight.prepare_humming_tensor_for_glu (pure torch) -> glu_order.npz
   * pack_weight_kernel / unpack_weight_kernel / dequant_unpacked_fp_type,
     the reference's CUDA kernel bodies compiled for the host
     (oracle/ref_host.cpp)                                       -> pack_bits.npz, decode_fp.npz
@@ -98,6 +99,19 @@ def golden_moe_align():
             cases[f"c{i}_expert_ids"] = expert_ids.numpy()
             cases[f"c{i}_num_tokens_post_padded"] = np.array(int(ntpp))
     np.savez_compressed(os.path.join(HERE, "moe_align.npz"), **cases)
+
+
+def golden_glu_order():
+    from humming.utils.weight import prepare_humming_tensor_for_glu
+
+    out = {}
+    for i, (shape, shape_n, pad, is_moe) in enumerate([((8, 3), 8, 0, False), ((12, 2), 12, 4, False), ((2, 16, 2), 16, 0, True),
+                                                       ((3, 20, 1), 20, 4, True)]):
+        t = torch.arange(int(np.prod(shape)), dtype=torch.int32).view(*shape)
+        out[f"c{i}_cfg"] = np.array([shape_n, pad, int(is_moe)])
+        out[f"c{i}_in"] = t.numpy()
+        out[f"c{i}_out"] = prepare_humming_tensor_for_glu(t, shape_n, pad, is_moe).numpy()
+    np.savez_compressed(os.path.join(HERE, "glu_order.npz"), **out)
 
 
 def golden_host_kernels():
@@ -245,4 +259,5 @@ if __name__ == "__main__":
     golden_dtypes()
     golden_host_kernels()
     golden_moe_align()
+    golden_glu_order()
     print("golden fixtures written to", HERE)

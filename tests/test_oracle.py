@@ -271,6 +271,17 @@ def test_e4m3_cast_of_the_oracle_is_the_saturating_round_to_nearest_even_convers
 
 
 # ---------------------------------------------------------------- host-side mirror of the reference interface
+def test_glu_row_order_matches_reference_golden():
+    from humming_b200.utils.weight import prepare_humming_tensor_for_glu
+
+    g = np.load(os.path.join(GOLD, "glu_order.npz"))
+    for i in range(4):
+        shape_n, pad, is_moe = (int(v) for v in g[f"c{i}_cfg"])
+        got = prepare_humming_tensor_for_glu(torch.from_numpy(g[f"c{i}_in"]), shape_n, pad, bool(is_moe))
+        assert np.array_equal(got.numpy(), g[f"c{i}_out"])
+    assert prepare_humming_tensor_for_glu(None, 8) is None
+
+
 def test_dtypes_match_reference_golden():
     gold = json.load(open(os.path.join(GOLD, "dtypes.json")))
     for name, rec in gold.items():

@@ -14,10 +14,14 @@ Pinning status
   own kernels compiled for the host from the reference tree
   (``oracle/build_ref.sh`` -> ``oracle/_ref``), see ``tests/test_oracle.py``, and
   against committed vectors made by that build (``tests/golden/``).
-* ``weight_ref`` / ``gemm_ref`` / ``moe_align_block_size`` / ``moe_ref``:
-  restate torch expressions of ``humming/utils/test.py`` and the reference's
-  tests; pinned by golden vectors generated by running those reference Python
-  expressions on CPU tensors (``tests/golden/make_golden.py``).
+* ``weight_ref_int`` and ``quantize_weight_int`` together: pinned against the
+  reference's ``generate_random_weight`` -> ``quantize_weight`` -> kernel chain
+  run unmodified on CPU tensors (the kernel launch served by the kernel's host
+  build), ``tests/golden/random_weight.npz``: codes, 16-bit scales, zero points and
+  ``weight_ref`` bit for bit.  ``moe_align_block_size``: pinned by vectors from
+  the reference's ``generate_random_moe_tensors`` run on CPU tensors.
+  ``gemm_ref`` / ``moe_ref`` restate the one-line torch expressions of the
+  reference's README and tests (an fp32 matmul, a per-expert loop).
 * ``effective_weight_16`` (what the tensor cores multiply by on the 16-bit paths):
   pinned, bit for bit, against the reference's register-level code --
   ``dequant_single`` / ``dequant_single_zero_point`` of

@@ -10,6 +10,10 @@ What is executed from the reference, unmodified:
   * humming.utils.test.generate_random_moe_tensors, with torch's
     factory functions redirected from "cuda:0" to the CPU       -> moe_align.npz
   * humming.utils.weight.prepare_humming_tensor_for_glu (pure torch) -> glu_order.npz
+  * humming.utils.test.generate_random_weight with humming.utils.weight.quantize_weight
+    underneath, unmodified, torch's factories redirected to the CPU and the one
+    CUDA launch inside (QuantWeightKernel) served by the same kernel's host build
+    (oracle/ref_host_quant.cpp)                                  -> random_weight.npz
   * pack_weight_kernel / unpack_weight_kernel / dequant_unpacked_fp_type,
     the reference's CUDA kernel bodies compiled for the host
     (oracle/ref_host.cpp)                                       -> pack_bits.npz, decode_fp.npz
@@ -112,6 +116,68 @@ def golden_glu_order():
         out[f"c{i}_in"] = t.numpy()
         out[f"c{i}_out"] = prepare_humming_tensor_for_glu(t, shape_n, pad, is_moe).numpy()
     np.savez_compressed(os.path.join(HERE, "glu_order.npz"), **out)
+
+
+RANDOM_WEIGHT_CASES = [("uint4", "float16", 128, False, None), ("uint4", "bfloat16", 128, True, None),
+                       ("int4", "bfloat16", 128, False, 2), ("uint8", "float16", 128, True, None),
+                       ("uint4", "bfloat16", 32, True, 3), ("int8", "float16", 128, False, None)]
+
+
+class _HostQuantWeightKernel:
+    """Stands in for humming.kernel.quant_weight.QuantWeightKernel: same constructor and call signature, the launch
+    replaced by the host build of the very kernel it would launch."""
+
+    def __init__(self, source_dtype, target_dtype, group_size, has_scale, use_e8m0_scale, has_dynamic_zero_point=False, **_):
+        assert str(source_dtype) == "float32" and has_scale and not use_e8m0_scale and target_dtype.is_integer_type
+        self.bits, self.signed = target_dtype.num_bits, int(target_dtype.is_signed)
+        self.group_size, self.zp = group_size, int(has_dynamic_zero_point)
+        self.lib = ctypes.CDLL(os.path.join(ROOT, "oracle", "_ref", "libhumming_ref_host_quant.so"))
+
+    def __call__(self, inputs, outputs=None, scales=None, zero_point=None):
+        assert inputs.is_contiguous() and outputs.dtype == torch.int32 and scales.dtype == torch.float32
+        groups = inputs.nelement() // self.group_size
+        zps = torch.zeros(groups, dtype=torch.int32)
+        ptr = lambda t: ctypes.c_void_p(t.data_ptr())
+        rc = self.lib.ref_quant_weight_f32(ptr(inputs), ptr(outputs), ptr(scales), ptr(zps), ctypes.c_long(groups),
+                                           self.group_size, self.bits, self.signed, self.zp)
+        assert rc == 0, rc
+        if zero_point is not None:
+            zero_point.copy_(zps.view_as(zero_point))
+        return outputs, scales, zero_point
+
+
+def golden_random_weight():
+    def cpu(fn):
+        def wrapped(*a, **k):
+            k.pop("device", None)
+            return fn(*a, **k)
+        return wrapped
+
+    patches = [mock.patch(f"torch.{name}", cpu(getattr(torch, name))) for name in ("randn", "rand", "empty", "empty_like")]
+    for p in patches:
+        p.start()
+    try:
+        from humming import dtypes as ref_dtypes
+        from humming.utils import test as ref_test
+        from humming.utils import weight as ref_weight
+
+        out = {}
+        with mock.patch.object(ref_weight, "QuantWeightKernel", _HostQuantWeightKernel):
+            for i, (b, s, g, zp, e) in enumerate(RANDOM_WEIGHT_CASES):
+                torch.manual_seed(500 + i)
+                w_orig, w_ref, q, scale, zero_point, gs = ref_test.generate_random_weight(
+                    8, 256, g, ref_dtypes.DataType.from_str(b), ref_dtypes.DataType.from_str(s), num_experts=e, has_dynamic_zp=zp)
+                assert gs is None
+                out[f"c{i}_weight_orig"] = w_orig.numpy()
+                out[f"c{i}_weight_ref"] = w_ref.numpy()
+                out[f"c{i}_codes"] = q.numpy()
+                out[f"c{i}_scale_bits"] = scale.view(torch.int16).numpy()
+                if zp:
+                    out[f"c{i}_zero_point"] = zero_point.numpy()
+        np.savez_compressed(os.path.join(HERE, "random_weight.npz"), **out)
+    finally:
+        for p in patches:
+            p.stop()
 
 
 def golden_host_kernels():
@@ -260,4 +326,5 @@ if __name__ == "__main__":
     golden_host_kernels()
     golden_moe_align()
     golden_glu_order()
+    golden_random_weight()
     print("golden fixtures written to", HERE)

@@ -224,6 +224,47 @@ def test_quantize_weight_matches_reference_code(bits, signed, group, zp):
         assert np.array_equal(z.reshape(-1), zps.astype(np.int32))
 
 
+RANDOM_WEIGHT_CASES = [("uint4", "float16", 128, False, None), ("uint4", "bfloat16", 128, True, None),
+                       ("int4", "bfloat16", 128, False, 2), ("uint8", "float16", 128, True, None),
+                       ("uint4", "bfloat16", 32, True, 3), ("int8", "float16", 128, False, None)]
+
+
+@pytest.mark.parametrize("i", range(len(RANDOM_WEIGHT_CASES)))
+def test_weight_generator_chain_matches_the_reference_run_on_cpu(i):
+    """Outputs of the reference's generate_random_weight (quantize_weight and its kernel underneath, run on the CPU
+    when the fixture was made): the oracle's quantizer reproduces codes, 16-bit scales and zero points from
+    weight_orig, its weight_ref_int reproduces weight_ref from them, and the library's quantize_weight returns the
+    same tensors -- all bit for bit."""
+    from humming_b200.utils.weight import quantize_weight
+
+    b, sdt, group, zp, experts = RANDOM_WEIGHT_CASES[i]
+    g = np.load(os.path.join(GOLD, "random_weight.npz"))
+    w_orig, w_ref, codes, scale_bits = (g[f"c{i}_{k}"] for k in ("weight_orig", "weight_ref", "codes", "scale_bits"))
+    zero_point = g[f"c{i}_zero_point"] if zp else None
+    b_dtype = dtypes.DataType.from_str(b)
+    bits, signed = b_dtype.num_bits, b_dtype.is_signed
+    torch_sdt = torch.float16 if sdt == "float16" else torch.bfloat16
+    scale = torch.from_numpy(scale_bits).view(torch_sdt)
+    assert w_orig.shape == ((experts, 8, 256) if experts else (8, 256))
+    unsigned = codes + (2 ** (bits - 1) if signed else 0)          # the reference hands signed types out as q - 2^(b-1)
+
+    q, s32, z = oracle.quantize_weight_int(w_orig, bits, group, zp)
+    assert np.array_equal(q, unsigned)
+    assert torch.equal(torch.from_numpy(s32).to(torch_sdt).view(torch.int16), scale.view(torch.int16))
+    if zp:
+        assert np.array_equal(z, zero_point)
+
+    ref = oracle.weight_ref_int(unsigned, scale.float().numpy(), group, bits, zero_point)
+    assert np.array_equal(ref.view(np.uint32), w_ref.view(np.uint32))
+
+    lq, ls, lz, _ = quantize_weight(torch.from_numpy(w_orig), dtype=dtypes.DataType.from_str(f"uint{bits}"),
+                                    scale_dtype=dtypes.DataType.from_str(sdt), group_size=group, has_dynamic_zp=zp)
+    assert np.array_equal(lq.numpy(), unsigned)
+    assert torch.equal(ls.view(torch.int16), scale.view(torch.int16))
+    if zp:
+        assert np.array_equal(lz.numpy(), zero_point)
+
+
 # ---------------------------------------------------------------- MoE alignment
 def test_moe_align_matches_golden():
     g = np.load(os.path.join(GOLD, "moe_align.npz"))

@@ -10,6 +10,8 @@ What is executed from the reference, unmodified:
   * humming.utils.test.generate_random_moe_tensors, with torch's
     factory functions redirected from "cuda:0" to the CPU       -> moe_align.npz
   * humming.utils.weight.prepare_humming_tensor_for_glu (pure torch) -> glu_order.npz
+  * humming.layer.HummingLayer constructed on the CPU: parameter and buffer
+    names, shapes, dtypes and the meta's derived names           -> layer_params.json
   * humming.utils.test.generate_random_weight with humming.utils.weight.quantize_weight
     underneath, unmodified, torch's factories redirected to the CPU and the one
     CUDA launch inside (QuantWeightKernel) served by the same kernel's host build
@@ -180,6 +182,49 @@ def golden_random_weight():
             p.stop()
 
 
+LAYER_CASES = {
+    # the benchmark configurations' layers, plus sublayer naming
+    "c1_dense_fp16_1024": dict(shape_n=1024, shape_k=1024, a_dtype="float16", b_dtype="uint4", c_dtype="float16", bs_dtype="float16",
+                               weight_scale_group_size=128),
+    "c2_gate_up_bf16_zp": dict(shape_n=28672, shape_k=4096, a_dtype="bfloat16", b_dtype="uint4", c_dtype="bfloat16",
+                               bs_dtype="bfloat16", weight_scale_group_size=128, has_dynamic_zp=True),
+    "c2_down_bf16_zp_bias": dict(shape_n=4096, shape_k=14336, a_dtype="bfloat16", b_dtype="uint4", c_dtype="bfloat16",
+                                 bs_dtype="bfloat16", weight_scale_group_size=128, has_dynamic_zp=True, has_bias=True,
+                                 sublayer_name="down"),
+    "c3_mxfp4_fp8": dict(shape_n=8192, shape_k=8192, a_dtype="float8e4m3", b_dtype="float4e2m1", c_dtype="bfloat16",
+                         bs_dtype="float8e8m0", weight_scale_group_size=32),
+    "c4_moe_up": dict(shape_n=1536, shape_k=2048, a_dtype="bfloat16", b_dtype="uint4", c_dtype="bfloat16", bs_dtype="bfloat16",
+                      weight_scale_group_size=128, num_experts=128),
+    "c4_moe_down": dict(shape_n=2048, shape_k=768, a_dtype="bfloat16", b_dtype="uint4", c_dtype="bfloat16", bs_dtype="bfloat16",
+                        weight_scale_group_size=128, num_experts=128),
+    "c5_moe_up_w4a8": dict(shape_n=4096, shape_k=7168, a_dtype="float8e4m3", b_dtype="uint4", c_dtype="bfloat16",
+                           bs_dtype="bfloat16", weight_scale_group_size=128, num_experts=4),
+    "channelwise_fp16": dict(shape_n=512, shape_k=1024, a_dtype="float16", b_dtype="uint4", c_dtype="float16", bs_dtype="float16",
+                             weight_scale_group_size=0),
+}
+
+
+def golden_layer_params():
+    from humming import dtypes as ref_dtypes
+    from humming.layer import HummingLayer
+
+    out = {}
+    for name, kwargs in LAYER_CASES.items():
+        typed = {k: ref_dtypes.DataType.from_str(v) if k.endswith("_dtype") else v for k, v in kwargs.items()}
+        with torch.device("meta"):          # shapes only: the MoE cases would hold gigabytes
+            layer = HummingLayer(**typed)
+        rec = {"kwargs": kwargs, "tensors": {}}
+        for n, t in list(layer.named_parameters()) + list(layer.named_buffers()):
+            rec["tensors"][n] = {"shape": list(t.shape), "dtype": str(t.dtype), "requires_grad": bool(t.requires_grad)}
+        m = layer.meta
+        rec["names"] = {k: getattr(m, k) for k in ("weight_name", "weight_scale_name", "zero_point_name", "bias_name",
+                                                    "global_scale_name") if hasattr(m, k)}
+        rec["has_input_scale"] = m.has_input_scale
+        out[name] = rec
+    with open(os.path.join(HERE, "layer_params.json"), "w") as f:
+        json.dump(out, f, indent=1, sort_keys=True)
+
+
 def golden_host_kernels():
     lib = ctypes.CDLL(os.path.join(ROOT, "oracle", "_ref", "libhumming_ref_host.so"))
     rng = np.random.default_rng(2024)
@@ -326,5 +371,6 @@ if __name__ == "__main__":
     golden_host_kernels()
     golden_moe_align()
     golden_glu_order()
+    golden_layer_params()
     golden_random_weight()
     print("golden fixtures written to", HERE)

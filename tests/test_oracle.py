@@ -346,6 +346,25 @@ def test_dtypes_match_reference_golden():
     assert dtypes.uint4 == dtypes.DataType.from_str("uint4") and hash(dtypes.uint4) == hash("uint4")
 
 
+def test_layer_parameters_match_the_reference_constructor_golden():
+    """Names, shapes, dtypes and requires_grad of every parameter and buffer, and the meta's derived names, as the
+    reference's own HummingLayer constructor creates them for the benchmark configurations' layers."""
+    from humming_b200.layer import HummingLayer
+
+    with open(os.path.join(GOLD, "layer_params.json")) as f:
+        gold = json.load(f)
+    assert len(gold) == 8
+    for name, rec in gold.items():
+        with torch.device("meta"):
+            layer = HummingLayer(**rec["kwargs"])
+        got = {n: {"shape": list(t.shape), "dtype": str(t.dtype), "requires_grad": bool(t.requires_grad)}
+               for n, t in list(layer.named_parameters()) + list(layer.named_buffers())}
+        assert got == rec["tensors"], name
+        for attr, value in rec["names"].items():
+            assert getattr(layer.meta, attr) == value, (name, attr)
+        assert layer.meta.has_input_scale == rec["has_input_scale"], name
+
+
 def test_layer_meta_and_parameter_shapes_follow_the_reference():
     from humming_b200.layer import HummingLayer, HummingLayerMeta
 

@@ -136,6 +136,10 @@ def _launch_cuda(configs, a, b, c=None, as_=None, bs=None, bzp=None, bias=None, 
     if num_sms is not None:
         desc.num_sms = int(num_sms)
     moe = desc.num_experts > 0
+    if moe and desc.flags & (native.HM_FLAG_MOE_A_SORTED | native.HM_FLAG_MOE_C_SORTED):
+        # those layouts need the token count as a separate argument, which this schema has no place for
+        raise NotImplementedError("pre-sorted MoE activations / outputs are reached through HummingLayer.forward "
+                                  "(inputs_sorted / outputs_sorted), not through launch_humming")
     if should_check_tensor:
         if rows.size(1) != desc.shape_k:
             raise ValueError(f"a has K={rows.size(1)}, the descriptor says {desc.shape_k}")

@@ -134,3 +134,16 @@ def test_operator_traces_into_an_fx_graph_with_fake_tensors():
     val = calls[0].meta["val"]
     assert tuple(val.shape) == (7, 1024) and val.dtype == torch.bfloat16 and val.device.type == "cuda"
     assert list(calls[0].args[0]) == configs
+
+
+def test_sorted_moe_layouts_are_refused_by_the_operator():
+    """The CUDA implementation rejects them before touching any tensor (called directly here: no GPU is present)."""
+    desc = runtime.make_desc(512, 1024, "bfloat16", "uint4", "bfloat16", "bfloat16", group_size=128, num_experts=8, top_k=2,
+                             flags=native.HM_FLAG_MOE_A_SORTED)
+    x = torch.zeros((4, 1024), dtype=torch.bfloat16)
+    with pytest.raises(NotImplementedError, match="inputs_sorted"):
+        ops._launch_cuda(ops.desc_to_configs(desc), x, x, locks=torch.zeros(64, dtype=torch.uint8))
+    with pytest.raises(ValueError, match="workspace"):
+        ops._launch_cuda(ops.desc_to_configs(desc), x, x)
+    with pytest.raises(NotImplementedError, match="global scale"):
+        ops._launch_cuda(ops.desc_to_configs(desc), x, x, gs=x, locks=torch.zeros(64, dtype=torch.uint8))

@@ -1,0 +1,40 @@
+"""How a kernel abort reaches the caller, with the failure injected on the host: the kernels' bounded waits write
+(code, CTA, detail, detail) into the first words of the workspace and return; ``hm_check_status`` turns that record
+into ``HM_ERR_DEVICE``, clears the workspace (counters and partial sums may be half-updated) and the layer is usable
+again.  No kernel is made to fail here: the record is written by the test."""
+import pytest
+import torch
+
+from helpers import build_layer
+from humming_b200 import native, runtime
+from humming_b200.utils import synthetic
+
+pytestmark = pytest.mark.gpu
+
+
+def test_abort_record_becomes_an_error_and_the_workspace_is_cleared(cuda_device):
+    ws = torch.zeros(1 << 16, dtype=torch.uint8, device=cuda_device)
+    runtime.check_status(ws)                                   # clean workspace: nothing to report
+    ws.view(torch.int32)[:4] = torch.tensor([5, 17, 3, 9], dtype=torch.int32, device=cuda_device)
+    ws[4096:4100] = 7                                          # leftovers of the aborted call further in
+    with pytest.raises(native.HummingError) as err:
+        runtime.check_status(ws)
+    assert err.value.code == native.HM_ERR_DEVICE
+    assert "code 5 in CTA 17" in str(err.value) and "3, 9" in str(err.value)
+    assert int(ws.count_nonzero()) == 0
+    runtime.check_status(ws)                                   # and the next check is clean again
+    with pytest.raises(native.HummingError):                   # too small to hold the record
+        runtime.check_status(torch.zeros(64, dtype=torch.uint8, device=cuda_device))
+
+
+def test_layer_recovers_after_a_reported_abort(cuda_device):
+    case = synthetic.dense_w4a16_case(1024, 1024, torch.float16, False, seed=81)
+    layer, _ = build_layer(case)
+    x = synthetic.activations(16, 1024, torch.float16, seed=82).to(cuda_device)
+    want = layer(inputs=x).clone()
+    layer.check_status()
+    layer.humming_workspace.view(torch.int32)[:4] = torch.tensor([2, 0, 1, 1], dtype=torch.int32, device=cuda_device)
+    with pytest.raises(native.HummingError, match="kernel aborted"):
+        layer.check_status()
+    assert torch.equal(layer(inputs=x), want)                  # same workspace, cleared by the failed check
+    layer.check_status()

@@ -253,11 +253,12 @@ def run_moe(args, rank, world, local_rank):
         for _ in range(max(args.warmup, 3)):
             step()
         moe.check_status()
-        if world == 1:
-            # One GPU: no host-side step in the layer, so a forward is captured once and replayed.
+        if world == 1 or (args.ep_graph and args.ep_mode == "replicate"):
+            # No host-side step in the layer (one GPU; replicated tokens: collectives with fixed shapes), so a
+            # forward is captured once and replayed.
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
-                moe(x, logits)
+                moe(x, logits, pad_to=pad_to)
             step = graph.replay
             step()
         if world > 1:
@@ -291,7 +292,7 @@ def run_moe(args, rank, world, local_rank):
                    "experts": experts, "top_k": top_k, "hidden": hidden, "intermediate": inter, "tokens_total": top["tokens"],
                    "parallelism": f"ep{world} ({args.ep_mode})" if world > 1 else "single GPU",
                    "timing": "one GPU: CUDA graph of a forward replayed K times; expert parallel: eager launches (dispatch mode reads the "
-                             "exchange sizes on the host every step, replicate mode reads nothing); CUDA events, max over ranks"},
+                             "exchange sizes on the host every step, replicate mode reads nothing" + (" and is replayed from a CUDA graph" if (world > 1 and args.ep_graph and args.ep_mode == "replicate") else "") + "); CUDA events, max over ranks"},
         "tflops": top["tokens_per_s"] * flops_per_token / 1e12,
         "sweep": results,
     }
@@ -578,6 +579,8 @@ def main():
     ap.add_argument("--workload", default="dense", choices=["dense", "moe", "moe-w4a8", "mxfp4"])
     ap.add_argument("--ep-mode", default="dispatch", choices=["dispatch", "replicate"],
                     help="moe workloads on more than one GPU: all-to-all dispatch / combine, or all-gather + reduce-scatter")
+    ap.add_argument("--ep-graph", action="store_true",
+                    help="with --ep-mode replicate: capture the layer, collectives included, in a CUDA graph")
     ap.add_argument("--tokens", default=None, help="moe workload: total token counts to time, the last one is the headline")
     ap.add_argument("--native-flags", type=int, default=0, help="HM_FLAG_* bits OR-ed into every dense GEMM descriptor (kernel A/B comparisons)")
     ap.add_argument("--point", default=None, help="PROJ:M, e.g. gate_up:16 -- launch only this sweep point a few times")

@@ -1,0 +1,114 @@
+"""Host logic of ``HummingMethod.load_weight`` on the CPU: N-shards of a fused weight (``offset_n``), one expert at
+a time (``expert_id``), several GEMMs on one module (``sublayer_name``) -- reference ``humming/layer.py:169-326``.
+The one device step inside, packing codes into words, is served here by the oracle's ``pack_bits`` (itself pinned
+against the reference's pack kernel), so that what is checked is where every shard lands in the parameters."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import oracle
+from humming_b200 import runtime
+from humming_b200.layer import HummingLayer, HummingLayerMeta, HummingMethod
+
+
+@pytest.fixture
+def host_pack(monkeypatch):
+    def pack(codes, bits, out=None):
+        words = oracle.pack_bits(codes.numpy().astype(np.uint32), bits).astype(np.uint32).view(np.int32)
+        return torch.from_numpy(words.copy()).view(*codes.shape[:-1], codes.size(-1) * bits // 32)
+
+    monkeypatch.setattr(runtime, "pack_weight", pack)
+    monkeypatch.setattr(torch.Tensor, "cuda", lambda self, *a, **k: self)
+
+
+def _case(n, k, experts=None, seed=0):
+    gen = torch.Generator().manual_seed(seed)
+    lead = (experts,) if experts else ()
+    codes = torch.randint(0, 16, lead + (n, k), generator=gen, dtype=torch.int32)
+    scales = (torch.randn(lead + (n, k // 128), generator=gen).abs() * 0.02 + 1e-3).bfloat16()
+    zps = torch.randint(0, 16, lead + (n, k // 128), generator=gen, dtype=torch.int32)
+    bias = torch.randn(lead + (n,), generator=gen).bfloat16()
+    return codes, scales, zps, bias
+
+
+def _layer(n, k, experts=None):
+    return HummingLayer(shape_n=n, shape_k=k, a_dtype="bfloat16", b_dtype="uint4", c_dtype="bfloat16", bs_dtype="bfloat16",
+                        weight_scale_group_size=128, has_dynamic_zp=True, has_bias=True, num_experts=experts)
+
+
+def _state(layer):
+    return {n: p.detach().clone() for n, p in layer.named_parameters()}
+
+
+def _same(a, b):
+    assert a.keys() == b.keys()
+    for name in a:
+        assert torch.equal(a[name].view(torch.uint8), b[name].view(torch.uint8)), name
+
+
+def test_shards_along_n_land_where_the_whole_tensor_does(host_pack):
+    n, k = 384, 256
+    codes, scales, zps, bias = _case(n, k)
+    whole = _layer(n, k)
+    whole.load_weight(weight=codes, weight_scale=scales, zero_point=zps, bias=bias)
+    parts = _layer(n, k)
+    for p in parts.parameters():
+        p.data.view(torch.uint8).fill_(0xAB)                    # every byte must be overwritten by some shard
+    for lo, hi in ((128, 384), (0, 128)):                       # a fused weight's parts, in any order
+        HummingMethod.load_weight(parts, weight=codes[lo:hi], weight_scale=scales[lo:hi], zero_point=zps[lo:hi],
+                                  bias=bias[lo:hi], offset_n=lo)
+    _same(_state(whole), _state(parts))
+    # the staged codes are the plain packing of the (N, K) codes
+    want = oracle.pack_bits(codes.numpy().astype(np.uint32), 4).astype(np.uint32).view(np.int32)
+    assert np.array_equal(whole.weight.data.view(-1).numpy(), want.reshape(-1))
+
+
+def test_experts_one_at_a_time_and_in_shards(host_pack):
+    e, n, k = 3, 256, 256
+    codes, scales, zps, bias = _case(n, k, experts=e, seed=1)
+    whole = _layer(n, k, e)
+    whole.load_weight(weight=codes, weight_scale=scales, zero_point=zps, bias=bias)
+    single = _layer(n, k, e)
+    for i in range(e):
+        single.load_weight(weight=codes[i], weight_scale=scales[i], zero_point=zps[i], bias=bias[i], expert_id=i)
+    _same(_state(whole), _state(single))
+    sharded = _layer(n, k, e)
+    for i in (2, 0, 1):
+        for lo in (128, 0):
+            HummingMethod.load_weight(sharded, weight=codes[i, lo:lo + 128], weight_scale=scales[i, lo:lo + 128],
+                                      zero_point=zps[i, lo:lo + 128], bias=bias[i, lo:lo + 128], offset_n=lo, expert_id=i)
+    _same(_state(whole), _state(sharded))
+
+
+def test_two_gemms_on_one_module(host_pack):
+    module = torch.nn.Module()
+    metas = {}
+    for name, (n, k) in {"qkv": (384, 256), "o": (256, 128)}.items():
+        metas[name] = HummingLayerMeta(a_dtype="bfloat16", b_dtype="uint4", c_dtype="bfloat16", bs_dtype="bfloat16", shape_n=n,
+                                       shape_k=k, weight_scale_group_size=128, has_dynamic_zp=True, sublayer_name=name)
+        HummingMethod.create_weights(module, metas[name])
+    assert {n for n, _ in module.named_parameters()} == {"qkv_weight", "qkv_weight_scale", "qkv_zero_point", "o_weight",
+                                                         "o_weight_scale", "o_zero_point"}
+    for name, (n, k) in {"qkv": (384, 256), "o": (256, 128)}.items():
+        codes, scales, zps, _ = _case(n, k, seed=len(name))
+        HummingMethod.load_weight(module, weight=codes, weight_scale=scales, zero_point=zps, sublayer_name=name)
+        alone = HummingLayer(shape_n=n, shape_k=k, a_dtype="bfloat16", b_dtype="uint4", c_dtype="bfloat16", bs_dtype="bfloat16",
+                             weight_scale_group_size=128, has_dynamic_zp=True)
+        alone.load_weight(weight=codes, weight_scale=scales, zero_point=zps)
+        for base in ("weight", "weight_scale", "zero_point"):
+            assert torch.equal(getattr(module, f"{name}_{base}").view(torch.uint8), getattr(alone, base).view(torch.uint8))
+    with pytest.raises(RuntimeError, match="finish_load"):
+        HummingMethod.forward_layer(module, torch.zeros((1, 256), dtype=torch.bfloat16), sublayer_name="qkv")
+
+
+def test_bad_shapes_and_unbuilt_options_are_refused(host_pack):
+    layer = _layer(256, 256)
+    codes, scales, zps, bias = _case(256, 256)
+    with pytest.raises(AssertionError):
+        layer.load_weight(weight=codes[:, :128])
+    with pytest.raises(AssertionError):
+        layer.load_weight(weight_scale=scales[:100])
+    with pytest.raises(ValueError, match="multiple of 32"):
+        HummingMethod.load_weight(layer, zero_point=zps[:8], offset_n=4)
+    with pytest.raises(NotImplementedError):
+        layer.load_weight(weight=codes, global_scale=torch.ones(1))

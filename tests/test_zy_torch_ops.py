@@ -117,3 +117,36 @@ def test_prepare_helpers_give_what_finish_load_stores(cuda_device):
     assert torch.equal(zps.reshape(-1), layer.zero_point.data.reshape(-1))
     assert torch.equal(prepare_humming_bias(bias.to(cuda_device)), layer.bias.data.reshape(-1))
     assert prepare_humming_zero_point(None, dtypes.uint4) is None and prepare_humming_bias(None) is None
+
+
+def test_sublayers_loaded_in_shards_forward_like_standalone_layers(cuda_device):
+    """Two GEMMs on one module (``sublayer_name``), the fused one loaded as three N-shards (``offset_n``): parameters
+    and outputs equal those of standalone layers loaded in one piece (reference humming/layer.py:169-326, :519-550)."""
+    from humming_b200.layer import HummingLayerMeta
+
+    shapes = {"qkv": (384, 256), "o": (256, 384)}
+    cases = {name: synthetic.dense_w4a16_case(n, k, torch.bfloat16, True, seed=90 + i)
+             for i, (name, (n, k)) in enumerate(shapes.items())}
+    module = torch.nn.Module()
+    for name, (n, k) in shapes.items():
+        HummingMethod.create_weights(module, HummingLayerMeta(
+            a_dtype="bfloat16", b_dtype="uint4", c_dtype="bfloat16", bs_dtype="bfloat16", shape_n=n, shape_k=k,
+            weight_scale_group_size=128, has_dynamic_zp=True, sublayer_name=name))
+    module.to(cuda_device)
+    qkv = cases["qkv"]
+    for lo in (256, 0, 128):                                     # v, q, k: any order
+        HummingMethod.load_weight(module, weight=qkv.codes[lo:lo + 128].to(cuda_device),
+                                  weight_scale=qkv.scales[lo:lo + 128].to(cuda_device),
+                                  zero_point=qkv.zero_points[lo:lo + 128].to(cuda_device), offset_n=lo, sublayer_name="qkv")
+    o = cases["o"]
+    HummingMethod.load_weight(module, weight=o.codes.to(cuda_device), weight_scale=o.scales.to(cuda_device),
+                              zero_point=o.zero_points.to(cuda_device), sublayer_name="o")
+    for name, (n, k) in shapes.items():
+        HummingMethod.finish_load(module, sublayer_name=name)
+        alone, _ = build_layer(cases[name])
+        for base in ("weight", "weight_scale", "zero_point"):
+            assert torch.equal(getattr(module, f"{name}_{base}").view(torch.uint8), getattr(alone, base).view(torch.uint8)), (name, base)
+        x = synthetic.activations(20, k, torch.bfloat16, seed=7).to(cuda_device)
+        got = HummingMethod.forward_layer(module, x, sublayer_name=name)
+        assert torch.equal(got, alone(inputs=x))
+    HummingMethod.check_status(module)

@@ -22,6 +22,7 @@ def generate_random_inputs(m: int, k: int, group_size: int = 0, dtype: dtypes.Da
     dtype = dtypes.DataType.from_str(dtype)
     g = group_size if group_size > 0 else k
     assert k % g == 0
+    torch.randn((m, k // g), dtype=torch.float32, device=DEVICE)  # the reference draws (and drops) this first: same seed, same data
     x = torch.randn((m, k), dtype=torch.float32, device=DEVICE)
     x = x * torch.rand((m, k // g), dtype=torch.float32, device=DEVICE).repeat_interleave(g, 1)
     x = x / x.std()

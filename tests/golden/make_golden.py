@@ -16,6 +16,8 @@ What is executed from the reference, unmodified:
     underneath, unmodified, torch's factories redirected to the CPU and the one
     CUDA launch inside (QuantWeightKernel) served by the same kernel's host build
     (oracle/ref_host_quant.cpp)                                  -> random_weight.npz
+  * humming.utils.test.generate_random_inputs for 16-bit activations, torch's
+    factories redirected to the CPU                              -> random_inputs.npz
   * pack_weight_kernel / unpack_weight_kernel / dequant_unpacked_fp_type,
     the reference's CUDA kernel bodies compiled for the host
     (oracle/ref_host.cpp)                                       -> pack_bits.npz, decode_fp.npz
@@ -177,6 +179,14 @@ def golden_random_weight():
                 if zp:
                     out[f"c{i}_zero_point"] = zero_point.numpy()
         np.savez_compressed(os.path.join(HERE, "random_weight.npz"), **out)
+
+        out = {}
+        for i, (m, k, g, name) in enumerate([(5, 256, 0, "float16"), (3, 512, 128, "bfloat16")]):
+            torch.manual_seed(700 + i)
+            x_orig, x_ref, x, x_scale = ref_test.generate_random_inputs(m, k, g, ref_dtypes.DataType.from_str(name))
+            assert x_scale is None
+            out[f"c{i}_orig"], out[f"c{i}_ref"], out[f"c{i}_bits"] = x_orig.numpy(), x_ref.numpy(), x.view(torch.int16).numpy()
+        np.savez_compressed(os.path.join(HERE, "random_inputs.npz"), **out)
     finally:
         for p in patches:
             p.stop()

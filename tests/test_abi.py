@@ -175,3 +175,52 @@ def test_schedule_of_an_moe_call_without_any_tile_is_empty(units_per_cta):
     plan.mode, plan.grid, plan.units_per_cta, plan.total_units = 1, 148, units_per_cta, 0
     for cta in (0, 1, 73, 147):
         assert _segments(plan, cta) == []
+
+
+def test_random_plans_cover_every_unit_exactly_once():
+    """Seeded sweep over shapes, token counts, SM counts, forced tiles, flags and dtype combinations: every plan the
+    library accepts launches no idle worker, covers every (tile, K-step) unit once and gives a worker at most two
+    partial tiles; decode plans split K into equal runs that cover it."""
+    import random
+
+    rng = random.Random(7)
+    combos = [(2, 0x104, 2, 2, 128, 1), (1, 0x104, 1, 1, 128, 0), (4, 7, 2, 6, 32, 0), (4, 0x204, 2, 2, 128, 0), (2, 0x104, 2, 2, 0, 0)]
+    flag_choices = [0, 0, 0, native.HM_FLAG_NO_SPLIT_K, native.HM_FLAG_NO_GEMV, native.HM_FLAG_NO_CTA_PAIR, native.HM_FLAG_CTA_PAIR,
+                    native.HM_FLAG_DECODE_KERNEL, native.HM_FLAG_A_OPERAND_SMEM]
+    checked = 0
+    for _ in range(500):
+        n = 128 * rng.choice([1, 2, 3, 5, 8, 12, 17, 32, 48, 100, 224])
+        k = 128 * rng.choice([1, 2, 3, 6, 8, 16, 32, 56, 112])
+        m = rng.choice([1, 2, 3, 4, 5, 8, 15, 16, 17, 31, 33, 64, 65, 100, 128, 129, 255, 256, 257, 500, 1000, 2047, 4096])
+        a, b, c, bs, g, zp = rng.choice(combos)
+        desc = _desc(shape_n=n, shape_k=k, num_sms=rng.choice([148, 148, 132, 64, 16]), flags=rng.choice(flag_choices),
+                     m_tile=rng.choice([0, 0, 0, 16, 32, 64, 128, 256]), a_dtype=a, b_dtype=b, c_dtype=c, bs_dtype=bs,
+                     group_size=g, has_zp=zp)
+        plan = native.Plan()
+        if native.lib.hm_gemm_plan(desc, m, plan) != native.HM_OK:
+            continue
+        checked += 1
+        assert plan.grid >= 1 and plan.workspace_bytes >= 256
+        if plan.mode == 2:
+            splits, steps = plan.grid // plan.n_tiles, plan.units_per_cta
+            assert plan.grid % plan.n_tiles == 0 and steps >= 1 and (splits - 1) * steps < plan.kb_per_tile <= splits * steps
+            continue
+        tiles, kb = plan.n_tiles * plan.m_tiles, plan.kb_per_tile
+        assert plan.total_units == tiles * kb
+        assert plan.grid <= desc.num_sms * (2 if (plan.m_tile <= 64 and not plan.cta_pair) else 1)
+        if tiles * kb > 200000:
+            continue                                   # the walk below is quadratic in Python; the plan itself was checked
+        covered = set()
+        for cta in range(plan.grid):
+            segs = _segments(plan, cta)
+            assert segs, "a launched worker has no work"
+            assert sum(s[3] for s in segs) <= 2
+            for tile, kb0, kb1, partial, _nseg, _first, slot in segs:
+                assert 0 <= tile < tiles and 0 <= kb0 < kb1 <= kb and partial == int(kb1 - kb0 < kb)
+                units = range(tile * kb + kb0, tile * kb + kb1)
+                assert covered.isdisjoint(units)
+                covered.update(units)
+                if partial:
+                    assert slot // 2 == cta
+        assert len(covered) == plan.total_units
+    assert checked > 300

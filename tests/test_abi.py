@@ -224,3 +224,43 @@ def test_random_plans_cover_every_unit_exactly_once():
                     assert slot // 2 == cta
         assert len(covered) == plan.total_units
     assert checked > 300
+
+
+def test_random_moe_schedules_cover_every_unit_exactly_once():
+    """The MoE kernel derives its schedule on the device from the padded token count: total = m_tiles * n_tiles *
+    K-steps, contiguous runs of max(ceil(total / grid), 2) units.  For random sizes, including totals far below
+    the grid (most workers idle) and zero: every unit once, at most two partial tiles per worker, the contributors
+    of a split tile are consecutive workers with distinct partial slots."""
+    import random
+
+    rng = random.Random(11)
+    checked = 0
+    for _ in range(600):
+        n_tiles, kb = rng.choice([1, 2, 6, 12, 16, 32, 56]), rng.choice([1, 2, 6, 16, 56])
+        m_tiles, grid = rng.choice([0, 1, 2, 3, 7, 20, 64, 300]), rng.choice([1, 2, 37, 148, 296])
+        total = m_tiles * n_tiles * kb
+        if total > 100000 or m_tiles * n_tiles > 3000 * grid:
+            continue
+        checked += 1
+        plan = native.Plan()
+        plan.m_tile, plan.n_tiles, plan.m_tiles, plan.kb_per_tile = 16, n_tiles, m_tiles, kb
+        plan.mode, plan.grid, plan.units_per_cta, plan.total_units = 1, grid, max(-(-total // grid), 2), total
+        covered, slots, by_tile = set(), set(), {}
+        for cta in range(grid):
+            segs = _segments(plan, cta)
+            assert sum(s[3] for s in segs) <= 2
+            for tile, kb0, kb1, partial, nseg, first, slot in segs:
+                assert 0 <= tile < m_tiles * n_tiles and 0 <= kb0 < kb1 <= kb and partial == int(kb1 - kb0 < kb)
+                units = range(tile * kb + kb0, tile * kb + kb1)
+                assert covered.isdisjoint(units)
+                covered.update(units)
+                if partial:
+                    assert slot // 2 == cta and slot not in slots
+                    slots.add(slot)
+                    by_tile.setdefault(tile, []).append((cta, nseg, first))
+        assert len(covered) == total
+        for parts in by_tile.values():
+            nseg, first = parts[0][1], parts[0][2]
+            assert all(p[1] == nseg and p[2] == first for p in parts)
+            assert sorted(p[0] for p in parts) == list(range(first, first + nseg))
+    assert checked > 300

@@ -241,6 +241,9 @@ def run_moe(args, rank, world, local_rank):
         moe.load_expert(local, gu, gus, dn, dns)
     moe.finish_load()
     results = []
+    sampler = ClockSampler(local_rank) if rank == 0 else None   # clocks of rank 0's GPU over the whole sweep
+    if sampler:
+        sampler.start()
     token_list = args.tokens or ("4096,16384,32768" if w4a8 else "1,32,512,4096")
     for total_tokens in [int(t) for t in token_list.split(",")]:
         tokens = total_tokens // world + (1 if rank < total_tokens % world else 0)
@@ -278,6 +281,7 @@ def run_moe(args, rank, world, local_rank):
         results.append({"tokens": total_tokens, "ms_per_step": float(t), "tokens_per_s": total_tokens / (float(t) * 1e-3)})
     if rank != 0:
         return
+    clocks = sampler.stop()
     top = results[-1]
     flops_per_token = 2.0 * top_k * (2 * inter * hidden + hidden * inter)
     line = {
@@ -294,6 +298,7 @@ def run_moe(args, rank, world, local_rank):
                    "timing": "one GPU: CUDA graph of a forward replayed K times; expert parallel: eager launches (dispatch mode reads the "
                              "exchange sizes on the host every step, replicate mode reads nothing" + (" and is replayed from a CUDA graph" if (world > 1 and args.ep_graph and args.ep_mode == "replicate") else "") + "); CUDA events, max over ranks"},
         "tflops": top["tokens_per_s"] * flops_per_token / 1e12,
+        "clocks": clocks,
         "sweep": results,
     }
     print(json.dumps(line), flush=True)

@@ -192,9 +192,11 @@ HM_API int hm_gemm(const hm_gemm_desc* desc, int64_t m, const void* a, int64_t l
  * numel + num_experts * (block - 1), rounded up to a multiple of block),
  * expert_ids[capacity / block], num_post_padded[1].  scratch:
  * hm_moe_align_scratch_ints(numel, num_experts) ints (one histogram per 1024
- * entries); at most 1024 experts.  The reference leaves this to the caller and
- * does it in a Python loop (humming/utils/test.py:154-183, "TODO:
- * moe_align_block_size cuda kernel"). */
+ * entries); at most 1024 experts.  Entries whose id lies outside
+ * [0, num_experts) appear nowhere in sorted_ids (experts held by another GPU,
+ * padding rows): the GEMMs then neither read nor write their rows.  The
+ * reference leaves this to the caller and does it in a Python loop
+ * (humming/utils/test.py:154-183, "TODO: moe_align_block_size cuda kernel"). */
 HM_API int hm_moe_align_block_size(const int32_t* topk_ids, int64_t numel, int num_experts, int block,
                                    int32_t* sorted_ids, int64_t capacity, int32_t* expert_ids,
                                    int32_t* num_post_padded, int32_t* scratch, void* stream);
